@@ -1,7 +1,10 @@
 """Fixed-size recurrent state per live sequence, beside the paged K / V of attention layers.
 
-A recurrent mixer (linear attention, retention, delta rule) keeps, per sequence, an fp32 matrix per head and - where it
-has short convolutions - the last few inputs of every convolved channel.  The pool holds `max_batch_size` slots per such
+A recurrent mixer (linear attention, retention, delta rule, selective state space, gated matrix memory, gated linear
+recurrence) keeps, per sequence, fp32 memories ("S" and, for the gated matrix memory, the normaliser "n" and the running
+maximum "m") and - where it has short convolutions - the last few inputs of every convolved channel ("conv", in the
+compute dtype).  A layer whose mixer is a pair of mixers holds the pages of its paged part and the state of its recurrent
+part.  The pool holds `max_batch_size` slots per such
 layer; a sequence takes a slot when it is admitted and gives it back when it ends.  Slots are not cleared: the kernels
 take the state of a sequence that has consumed no token yet as zero.
 
@@ -41,6 +44,9 @@ def layer_cache_shapes(model_config, layer: int, num_blocks: int, block_size: in
         kv = max(getattr(model_config, "num_key_value_heads", model_config.num_attention_heads) // tp_size, 1)
         shp = (num_blocks, block_size, kv, model_config.head_dim)
         return shp, shp
+    sp = sp.paged_part
+    if sp is None:
+        return None
     if sp.kind == "latent":
         return (num_blocks, block_size, 1, sp.kv_rank + sp.rot_dim), None
     if sp.kind != "attention":
@@ -49,11 +55,20 @@ def layer_cache_shapes(model_config, layer: int, num_blocks: int, block_size: in
 
 
 def layer_state_shapes(model_config, layer: int, slots: int) -> Optional[Dict[str, Tuple[int, ...]]]:
-    """Shapes of a recurrent layer's state tensors ("S": fp32 memory, "conv": carried convolution inputs)."""
+    """Shapes of a recurrent layer's state tensors ("S", "n", "m": fp32 memories; "conv": carried convolution inputs in
+    the compute dtype)."""
     sp = _spec(model_config, layer)
-    if sp is None or not sp.recurrent:
+    sp = None if sp is None else sp.recurrent_part
+    if sp is None:
         return None
+    if sp.kind == "rglru":
+        return {"S": (slots, sp.lru_width), "conv": (slots, max(sp.conv - 1, 0), sp.lru_width)}
+    if sp.kind == "ssd":
+        return {"S": (slots, sp.heads, sp.state, sp.vdim),
+                "conv": (slots, max(sp.conv - 1, 0), sp.heads * sp.vdim + 2 * sp.groups * sp.state)}
     out = {"S": (slots, sp.heads, sp.dim, sp.vdim)}
+    if sp.kind == "mlstm":
+        out["n"], out["m"] = (slots, sp.heads, sp.dim), (slots, sp.heads)
     if sp.kind == "channel_delta":        # a one-tap convolution carries nothing: an empty tensor keeps the call uniform
         out["conv"] = (slots, max(sp.conv - 1, 0), 2 * sp.kv_heads * sp.dim + sp.heads * sp.vdim)
     return out
@@ -69,7 +84,7 @@ class StateCacheManager:
         for i in cache_layers(model_config):                  # models without recurrent layers only use the slot ids
             shapes = layer_state_shapes(model_config, i, self.num_slots)
             self.states.append(None if shapes is None else {
-                n: torch.zeros(s, dtype=torch.float32 if n == "S" else self.dtype, device=self.device)
+                n: torch.zeros(s, dtype=self.dtype if n.startswith("conv") else torch.float32, device=self.device)
                 for n, s in shapes.items()})
 
     @property

@@ -114,15 +114,16 @@ class PagedKVRuntime:
 
     def attend_ragged(self, layer_idx: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float,
                       bias_table=None, bucket_starts=None, sink: bool = False, v_other=None,
-                      lam: float = 0.0, lut=None) -> torch.Tensor:
+                      lam: float = 0.0, lut=None, mask_block: int = 0) -> torch.Tensor:
         """Write the step's K / V rows (values optionally blended with `v_other`) into the layer's pages, then attend
-        every step token over positions 0..pos of its sequence.  q [T, H x dim], k [T, G x dim], v [T, G x vdim]."""
+        every step token over positions 0..pos of its sequence (with `mask_block`: over the positions of its own block
+        of that many positions only).  q [T, H x dim], k [T, G x dim], v [T, G x vdim]."""
         from ...ops import mixers as mops
 
         kc, vc = self.k_caches[self.cache_index(layer_idx)], self.v_caches[self.cache_index(layer_idx)]
         mops.paged_kv_write_mix(k, v, kc, vc, self.block_tables, self.ragged, v_other=v_other, lam=lam)
         return mops.paged_bias_attention(q, kc, vc, self.block_tables, self.ragged, scale, bias_table=bias_table,
-                                         bucket_starts=bucket_starts, sink=sink, lut=lut)
+                                         bucket_starts=bucket_starts, sink=sink, lut=lut, mask_block=mask_block)
 
     @classmethod
     def scratch(cls, cfg, batch: int, seqlen: int, device, dtype, block_size: int = 16) -> "PagedKVRuntime":
@@ -138,7 +139,8 @@ class PagedKVRuntime:
             vs.append(None if shp is None or shp[1] is None else torch.zeros(shp[1], dtype=dtype, device=device))
             st = layer_state_shapes(cfg, i, batch)
             states.append(None if st is None else {
-                n: torch.zeros(sh, dtype=torch.float32 if n == "S" else dtype, device=device) for n, sh in st.items()})
+                n: torch.zeros(sh, dtype=dtype if n.startswith("conv") else torch.float32, device=device)
+                for n, sh in st.items()})
         rt = cls(ks, vs, block_size, states)
         tables = torch.arange(batch * per, dtype=torch.int32).view(batch, per)
         rt.set_ragged_step(tables, [seqlen] * batch, [0] * batch, list(range(batch)), device)

@@ -46,7 +46,26 @@ class MixerSpec:
                        `rot_dim` rotated channels; only the latent and the rotated part are cached.
     kind "retention":  outer-product memory per head with one scalar `decay` per head, rotary positions on the first
                        `rot_dims` channels of q and k (base `rot_base`), k scaled by dim^-1/2, no softmax; the read-out
-                       is brought to unit RMS per head and gated."""
+                       is brought to unit RMS per head and gated.
+    kind "mlstm":      matrix memory with exponential gating: per head a log input gate and a log forget gate (both
+                       soft-capped at `gate_cap`), a running maximum that keeps the exponentials bounded, a normaliser
+                       vector beside the matrix; the read-out is divided by max(|n . q|, exp(-m)), brought to unit RMS
+                       per head, weighted and gated by a sigmoid.
+    kind "ssd":        selective state space (state-space duality form): `heads` x `vdim` inner channels, `state` rows per
+                       head, B / C shared by `groups` of heads, a causal convolution of `conv` taps (with bias) and silu
+                       on x | B | C, step size softplus(dt + bias), decay exp(-exp(A_log) dt), skip D x, the output gated by
+                       silu(z) BEFORE an RMS norm in `norm_groups` parts.
+    kind "rglru":      gated linear recurrent unit per channel (`lru_width` channels, gates from block-diagonal matrices of
+                       `blocks` blocks, decay exp(-`lru_c` r softplus(lam))) behind a causal convolution of `conv` taps,
+                       multiplied by a tanh-GELU branch.
+    kind "pair":       several mixers side by side that read the same input (`parts`); every part's output is RMS-normed
+                       over the model width with a weight of its own and the results are averaged.
+
+    kind "attention" also takes: rotary positions on the first `rot_dims` channels of every q / k head (pairs (2i, 2i + 1)
+    when `rot_interleaved`, else (i, i + rot_dims / 2)); `head_unit_norm` (q and k divided by their root mean square over
+    the head, after the rotation, no weight); `mask_block` (a position sees only the keys of its own block of that many
+    positions, counted from the start of the sequence); `out_gate` (heads times sigmoid(W_g x) before the output
+    projection)."""
 
     kind: str = "attention"
     heads: int = 1
@@ -68,6 +87,18 @@ class MixerSpec:
     rot_dim: int = 0                  # width of the decoupled rotated q / k part (latent attention)
     rot_dims: int = 0                 # channels of a head that rotary positions turn (rotate-half pairs)
     rot_base: float = 10000.0
+    rot_interleaved: bool = False     # rotary pairs are (2i, 2i + 1) instead of (i, i + rot_dims / 2)
+    head_unit_norm: bool = False      # q, k / rms over the head (after the rotation), no weight
+    mask_block: int = 0               # > 0: keys of the query's own block of this many positions only
+    out_gate: bool = False            # heads * sigmoid(W_g x) in front of the output projection
+    gate_cap: float = 0.0             # mlstm: soft cap of the gate pre-activations (0 = none)
+    state: int = 0                    # ssd: rows of a head's state
+    groups: int = 1                   # ssd: groups of heads that share B / C
+    norm_groups: int = 1              # ssd: parts of the gated RMS norm
+    lru_width: int = 0                # rglru: channels
+    blocks: int = 1                   # rglru: blocks of the gate matrices
+    lru_c: float = 8.0                # rglru: decay = exp(-lru_c * r * softplus(lam))
+    parts: Optional[List["MixerSpec"]] = None      # pair: the mixers that run side by side
 
     def __post_init__(self) -> None:
         if self.kv_heads is None:
@@ -75,14 +106,35 @@ class MixerSpec:
         if self.vdim is None:
             self.vdim = self.dim
         assert self.heads % self.kv_heads == 0, "query heads must be a multiple of key/value heads"
+        if self.parts is not None:
+            self.parts = [MixerSpec(**p) if isinstance(p, dict) else p for p in self.parts]
+            assert sum(p.paged for p in self.parts) <= 1 and sum(p.recurrent for p in self.parts) <= 1, \
+                "a pair holds at most one paged and one recurrent mixer (they share the layer's pages / state slot)"
 
     @property
     def recurrent(self) -> bool:
-        return self.kind in ("lightning", "channel_delta", "retention")
+        if self.kind == "pair":
+            return any(p.recurrent for p in self.parts)
+        return self.kind in ("lightning", "channel_delta", "retention", "mlstm", "ssd", "rglru")
 
     @property
     def paged(self) -> bool:
+        if self.kind == "pair":
+            return any(p.paged for p in self.parts)
         return self.kind in ("attention", "latent")
+
+    @property
+    def paged_part(self) -> Optional["MixerSpec"]:
+        """The mixer that owns the layer's pages (itself, or the paged part of a pair)."""
+        if self.kind == "pair":
+            return next((p for p in self.parts if p.paged), None)
+        return self if self.paged else None
+
+    @property
+    def recurrent_part(self) -> Optional["MixerSpec"]:
+        if self.kind == "pair":
+            return next((p for p in self.parts if p.recurrent), None)
+        return self if self.recurrent else None
 
 
 @dataclass
@@ -181,7 +233,7 @@ class ModelConfig:
         if self.layer_specs is not None:
             self.layer_specs = [LayerSpec(**s) if isinstance(s, dict) else s for s in self.layer_specs]
             self.num_hidden_layers = len(self.layer_specs)
-            att = [s.mixer for s in self.layer_specs if s.mixer.paged] or [self.layer_specs[0].mixer]
+            att = [s.mixer.paged_part for s in self.layer_specs if s.mixer.paged] or [self.layer_specs[0].mixer]
             self.num_attention_heads, self.num_key_value_heads, self.head_dim = att[0].heads, att[0].kv_heads, att[0].dim
         if self.num_key_value_heads is None:
             self.num_key_value_heads = self.num_attention_heads

@@ -7,7 +7,15 @@
   * `ChannelDeltaMixer`: gated delta rule with a decay per head and key channel and short causal convolutions;
   * `LatentAttention`: softmax attention whose keys / values are rebuilt from one small normalised latent per token plus
     one rotated key part shared by all heads - only those are cached, and the attention runs in the latent space;
-  * `Retention`: decayed outer-product memory per head with rotary positions on q / k, no softmax, unit-RMS gated read-out.
+  * `Retention`: decayed outer-product memory per head with rotary positions on q / k, no softmax, unit-RMS gated read-out;
+  * `MatrixLSTM`: matrix memory with exponential input / forget gates, a running maximum and a normaliser vector;
+  * `SelectiveStateSpace`: state space with input-dependent step sizes behind a causal convolution, gate before the norm;
+  * `GatedLinearRecurrence`: per-channel real-gated linear recurrent unit behind a causal convolution, times a GELU branch;
+  * `MixerPair`: mixers side by side on the same input; their RMS-normed outputs are averaged.
+
+`BiasSinkAttention` also covers plain paged softmax attention with rotary positions (half or interleaved pairs, on a part
+of the head), a weightless unit norm of q / k heads, a block mask (a position sees its own block of positions only) and a
+sigmoid output gate: every one of these is a field of the `MixerSpec`.
 
 Every mixer keeps the call signature of `Attention` (`forward(x, meta, rope, kv_cache)`) and is selected per layer by
 `ModelConfig.layer_specs[i].mixer.kind` (`build_mixer`).  `kv_cache` is the step runtime (`inference.modeling.PagedKVRuntime`):
@@ -26,7 +34,8 @@ from .. import ops
 from ..ops import mixers as mops
 from .config import MixerSpec, ModelConfig
 
-__all__ = ["BiasSinkAttention", "LightningAttention", "ChannelDeltaMixer", "LatentAttention", "Retention", "build_mixer"]
+__all__ = ["BiasSinkAttention", "LightningAttention", "ChannelDeltaMixer", "LatentAttention", "Retention", "MatrixLSTM",
+           "SelectiveStateSpace", "GatedLinearRecurrence", "MixerPair", "build_mixer"]
 
 
 class _MixerBase(nn.Module):
@@ -52,7 +61,10 @@ class BiasSinkAttention(_MixerBase):
     def __init__(self, cfg: ModelConfig, spec: MixerSpec, layer_idx: int) -> None:
         super().__init__(cfg, spec, layer_idx)
         H, G, d, dv = spec.heads, spec.kv_heads, spec.dim, spec.vdim
-        self.qkv_proj = nn.Linear(cfg.hidden_size, H * d + G * d + G * dv, bias=spec.bias)
+        assert spec.rot_dims % 2 == 0 and spec.rot_dims <= d
+        # q | k | v (| output gate): one GEMM reads the layer input
+        self.qkv_proj = nn.Linear(cfg.hidden_size, H * d + G * d + G * dv + (H * dv if spec.out_gate else 0),
+                                  bias=spec.bias)
         if spec.proj_norm:
             self.q_norm_weight = nn.Parameter(torch.ones(H * d))
             self.k_norm_weight = nn.Parameter(torch.ones(G * d))
@@ -67,7 +79,12 @@ class BiasSinkAttention(_MixerBase):
         sp, eps = self.spec, self.cfg.norm_eps
         H, G, d, dv = sp.heads, sp.kv_heads, sp.dim, sp.vdim
         qkv = self.qkv_proj(x)
-        q, k, v = qkv.split([H * d, G * d, G * dv], dim=-1)
+        q, k, v, gate = qkv.split([H * d, G * d, G * dv, H * dv if sp.out_gate else 0], dim=-1)
+        if sp.rot_dims or sp.head_unit_norm:
+            # q and k heads sit side by side in the projection: rotated and normalised in place, in one launch
+            table = mops.rotary_table(kv_cache.max_len_host, sp.rot_dims, sp.rot_base, x.device) if sp.rot_dims else None
+            mops.rotary_unit_norm(qkv, H + G, d, sp.rot_dims, sp.rot_interleaved, table, kv_cache.ragged.token_pos,
+                                  eps if sp.head_unit_norm else None)
         if sp.proj_norm:
             q = ops.rms_norm(q.contiguous(), self.q_norm_weight, eps)
             k = ops.rms_norm(k.contiguous(), self.k_norm_weight, eps)
@@ -87,7 +104,9 @@ class BiasSinkAttention(_MixerBase):
             lut = self._aux("lut", x.device, lambda: mops.bucket_lut(
                 mops.log_bucket_starts(sp.bias_buckets, sp.bias_max)))
         o = kv_cache.attend_ragged(self.layer_idx, q, k, v, self.scale, bias_table=table, bucket_starts=starts,
-                                   sink=sp.sink, v_other=v_other, lam=lam, lut=lut)
+                                   sink=sp.sink, v_other=v_other, lam=lam, lut=lut, mask_block=sp.mask_block)
+        if sp.out_gate:
+            o = mops.sigmoid_gate_mul(o, gate)
         return self.o_proj(o)
 
 
@@ -216,12 +235,139 @@ class Retention(_MixerBase):
         return self.o_proj(o)
 
 
+class MatrixLSTM(_MixerBase):
+    """Per head a matrix S [dim, vdim], a normaliser n [dim] and a running maximum m, all zero at the start of a sequence
+    and carried in fp32.  With cap(z) = gate_cap tanh(z / gate_cap): i = cap(W_i h + b_i), f = logsigmoid(cap(W_f h + b_f)),
+    m' = max(f + m, i), S <- exp(f + m - m') S + exp(i - m') outer(k, v), n likewise with k alone; the read-out
+    S^T q / (max(|n . q|, exp(-m')) + 1e-6), q scaled by dim^-1/2, is brought to unit RMS per head, multiplied by a weight
+    over all heads' channels and by sigmoid(W_g h), and projected."""
+
+    def __init__(self, cfg: ModelConfig, spec: MixerSpec, layer_idx: int) -> None:
+        super().__init__(cfg, spec, layer_idx)
+        H, d, dv = spec.heads, spec.dim, spec.vdim
+        self.in_proj = nn.Linear(cfg.hidden_size, 2 * H * d + 2 * H * dv + 2 * H, bias=False)   # q | k | v | gate | i | f
+        self.gate_bias = nn.Parameter(torch.zeros(2 * H))                                       # b_i | b_f
+        self.norm_weight = nn.Parameter(torch.ones(H * dv))
+        self.o_proj = nn.Linear(H * dv, cfg.hidden_size, bias=False)
+
+    def forward(self, x: torch.Tensor, meta, rope=None, kv_cache=None) -> torch.Tensor:
+        sp = self.spec
+        H, d, dv = sp.heads, sp.dim, sp.vdim
+        z = self.in_proj(x)
+        q, k, v, g, gates = z.split([H * d, H * d, H * dv, H * dv, 2 * H], dim=-1)
+        bias = self._aux("gate_bias", x.device, lambda: self.gate_bias.detach().float())
+        st = kv_cache.layer_state(self.layer_idx)
+        o = mops.state_scan_mlstm(q, k, v, gates, bias, sp.gate_cap, st["S"], st["n"], st["m"], kv_cache.ragged, H, d, dv,
+                                  q_scale=d ** -0.5)
+        o = mops.gated_group_rms_norm(o, self.norm_weight, g, dv, self.cfg.norm_eps, x.dtype)
+        return self.o_proj(o)
+
+
+class SelectiveStateSpace(_MixerBase):
+    """inner = heads x vdim channels, `state` rows per head, B / C shared by `groups` of heads.  W_in h = [z | x | B | C | dt];
+    x | B | C pass a causal convolution (with bias) and silu; step = softplus(dt + dt_bias); per head
+    S <- exp(-exp(A_log) step) S + step outer(B, x), y = S^T C + D x, S [state, vdim] zero at the start and carried in fp32
+    together with the convolution's last inputs.  y silu(z) is RMS-normed in `norm_groups` parts, weighted and projected."""
+
+    def __init__(self, cfg: ModelConfig, spec: MixerSpec, layer_idx: int) -> None:
+        super().__init__(cfg, spec, layer_idx)
+        H, dv, N, G = spec.heads, spec.vdim, spec.state, spec.groups
+        self.inner = H * dv
+        assert H % G == 0 and self.inner % spec.norm_groups == 0
+        self.conv_channels = self.inner + 2 * G * N
+        self.in_proj = nn.Linear(cfg.hidden_size, self.inner + self.conv_channels + H, bias=False)
+        self.conv_weight = nn.Parameter(torch.zeros(self.conv_channels, max(spec.conv, 1)))
+        self.conv_bias = nn.Parameter(torch.zeros(self.conv_channels))
+        self.dt_bias = nn.Parameter(torch.zeros(H))
+        self.A_log = nn.Parameter(torch.zeros(H))
+        self.D = nn.Parameter(torch.ones(H))
+        self.norm_weight = nn.Parameter(torch.ones(self.inner))
+        self.o_proj = nn.Linear(self.inner, cfg.hidden_size, bias=False)
+
+    def forward(self, x: torch.Tensor, meta, rope=None, kv_cache=None) -> torch.Tensor:
+        sp = self.spec
+        H, dv, N, G = sp.heads, sp.vdim, sp.state, sp.groups
+        zz = self.in_proj(x)
+        z, xbc, dt = zz.split([self.inner, self.conv_channels, H], dim=-1)
+        st = kv_cache.layer_state(self.layer_idx)
+        ragged = kv_cache.ragged
+        xbc = mops.short_conv_silu(xbc, self.conv_weight, st["conv"], ragged, bias=self.conv_bias)
+        xs, b, c = xbc.split([self.inner, G * N, G * N], dim=-1)
+        f32 = lambda name: self._aux(name, x.device, lambda: getattr(self, name).detach().float())
+        y = mops.state_scan_ssd(c, b, xs, dt, f32("dt_bias"), f32("A_log"), f32("D"), st["S"], ragged, H, G, N, dv)
+        y = mops.gated_group_rms_norm(y, self.norm_weight, z, self.inner // sp.norm_groups, self.cfg.norm_eps, x.dtype,
+                                      gate_act="silu", gate_first=True)
+        return self.o_proj(y)
+
+
+class GatedLinearRecurrence(_MixerBase):
+    """Two branches of `lru_width` channels: y = gelu_tanh(W_y h + b_y) and u = conv(W_x h + b_x) (causal, per channel,
+    with bias, no activation).  u is cut into `blocks` parts; in part b, r = sigmoid(A_b u_b + a_b), i = sigmoid(I_b u_b +
+    i_b); log a = -lru_c r softplus(lam); S <- a S + sqrt(1 - a^2) i u per channel, zero at the start and carried in fp32
+    together with the convolution's last inputs; the output is W_o (S y).  The gate matrices' products keep their fp32
+    accumulators (no 16-bit rounding in front of the sigmoids)."""
+
+    def __init__(self, cfg: ModelConfig, spec: MixerSpec, layer_idx: int) -> None:
+        super().__init__(cfg, spec, layer_idx)
+        C, nb = spec.lru_width, spec.blocks
+        assert C % nb == 0
+        bw = C // nb
+        self.in_proj = nn.Linear(cfg.hidden_size, 2 * C, bias=True)                      # y branch | x branch
+        self.conv_weight = nn.Parameter(torch.zeros(C, max(spec.conv, 1)))
+        self.conv_bias = nn.Parameter(torch.zeros(C))
+        self.gate_weight = nn.Parameter(torch.zeros(nb, 2 * bw, bw))                     # per block: recurrence gate | input gate
+        self.gate_bias = nn.Parameter(torch.zeros(nb, 2 * bw))
+        self.lam = nn.Parameter(torch.zeros(C))
+        self.o_proj = nn.Linear(C, cfg.hidden_size, bias=False)
+        nn.init.normal_(self.gate_weight, std=cfg.initializer_range)
+
+    def forward(self, x: torch.Tensor, meta, rope=None, kv_cache=None) -> torch.Tensor:
+        sp = self.spec
+        C, nb = sp.lru_width, sp.blocks
+        T = x.shape[0]
+        z = self.in_proj(x)
+        branch, xb = z[:, :C], z[:, C:]
+        st = kv_cache.layer_state(self.layer_idx)
+        ragged = kv_cache.ragged
+        u = mops.short_conv_silu(xb, self.conv_weight, st["conv"], ragged, activation=False, bias=self.conv_bias)
+        ub = u.view(T, nb, C // nb).transpose(0, 1)                                      # [blocks, T, bw]
+        wt = self.gate_weight.transpose(1, 2)                                            # [blocks, bw, 2 bw]
+        if u.is_cuda and u.dtype != torch.float32:
+            gates = torch.bmm(ub, wt, out_dtype=torch.float32)
+        else:
+            gates = torch.bmm(ub.float(), wt.float())
+        f32 = lambda name: self._aux(name, x.device, lambda: getattr(self, name).detach().float().contiguous())
+        s = mops.lru_scan(u, gates.contiguous(), f32("gate_bias"), f32("lam"), branch, st["S"], ragged, c=sp.lru_c)
+        return self.o_proj(s)
+
+
+class MixerPair(nn.Module):
+    """Mixers side by side: every part reads the same input, its output is RMS-normed over the model width with a plain
+    weight of its own, and the results are averaged (in fp32: the sum goes straight into the residual stream).  The paged
+    part uses the layer's pages, the recurrent part the layer's state slot."""
+
+    def __init__(self, cfg: ModelConfig, spec: MixerSpec, layer_idx: int) -> None:
+        super().__init__()
+        self.cfg, self.spec, self.layer_idx = cfg, spec, layer_idx
+        self.shard_config = None
+        self.parts = nn.ModuleList([_build(cfg, p, layer_idx) for p in spec.parts])
+        self.out_norm_weights = nn.ParameterList([nn.Parameter(torch.ones(cfg.hidden_size)) for _ in spec.parts])
+
+    def forward(self, x: torch.Tensor, meta, rope=None, kv_cache=None) -> torch.Tensor:
+        outs = [m(x, meta, rope, kv_cache) for m in self.parts]
+        return mops.norm_mean(outs, list(self.out_norm_weights), self.cfg.norm_eps)
+
+
 _KINDS = {"attention": BiasSinkAttention, "lightning": LightningAttention, "channel_delta": ChannelDeltaMixer,
-          "latent": LatentAttention, "retention": Retention}
+          "latent": LatentAttention, "retention": Retention, "mlstm": MatrixLSTM, "ssd": SelectiveStateSpace,
+          "rglru": GatedLinearRecurrence, "pair": MixerPair}
 
 
-def build_mixer(cfg: ModelConfig, layer_idx: int) -> nn.Module:
-    spec = cfg.layer_specs[layer_idx].mixer
+def _build(cfg: ModelConfig, spec: MixerSpec, layer_idx: int) -> nn.Module:
     if spec.kind not in _KINDS:
         raise ValueError(f"unknown mixer kind {spec.kind!r}; known: {sorted(_KINDS)}")
     return _KINDS[spec.kind](cfg, spec, layer_idx)
+
+
+def build_mixer(cfg: ModelConfig, layer_idx: int) -> nn.Module:
+    return _build(cfg, cfg.layer_specs[layer_idx].mixer, layer_idx)

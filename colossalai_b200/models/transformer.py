@@ -374,6 +374,8 @@ class DecoderLayer(nn.Module):
             return self.post_attention_layernorm(x + self.mlp(x))
         if cfg.parallel_block and cfg.fp32_residual:
             return self._forward_parallel_stream(x, meta, rope, kv_cache)
+        if cfg.fp32_residual:
+            return self._forward_pre_stream(x, meta, rope, kv_cache)
         if cfg.parallel_block:
             h = self.input_layernorm(x)
             return x + self.self_attn(h, meta, rope, kv_cache) + self.mlp(h)
@@ -401,6 +403,21 @@ class DecoderLayer(nn.Module):
             y = self.mlp(h)
             outs += [t for t in (y if isinstance(y, tuple) else (y,)) if t is not None]
         meta.pending = outs
+        return x
+
+    def _forward_pre_stream(self, x: torch.Tensor, meta: SeqMeta, rope, kv_cache) -> torch.Tensor:
+        """Pre-norm sublayers on an fp32 stream: x <- x + mixer(norm1(x)); x <- x + ff(norm2(x)).  Each sublayer's output
+        is left PENDING and added, in fp32, by the kernel that normalises the stream for the next sublayer (this
+        layer's second norm, the next layer's first one, or the final norm): one pass over x per sublayer."""
+        cfg = self.cfg
+        kw = dict(eps=cfg.norm_eps, kind=cfg.norm_type, offset=cfg.norm_weight_offset)
+        h = ops.mixers.stream_add_norm(x, meta.pending or (), row=meta.pending_row, weight=self.input_layernorm.weight, **kw)
+        meta.pending_row = None
+        meta.pending = [self.self_attn(h, meta, rope, kv_cache)]
+        if self.mlp is not None:
+            h = ops.mixers.stream_add_norm(x, meta.pending, weight=self.post_attention_layernorm.weight, **kw)
+            y = self.mlp(h)
+            meta.pending = [t for t in (y if isinstance(y, tuple) else (y,)) if t is not None]
         return x
 
     def _forward_sublayer_out(self, x: torch.Tensor, meta: SeqMeta, rope, kv_cache) -> torch.Tensor:
@@ -600,7 +617,7 @@ class TransformerModel(nn.Module):
                                               else self.embed_tokens.weight.dtype)
         start, end = self.layer_range()
         n_ckpt = self._num_ckpt_layers(end - start) if self.training else 0
-        stream = cfg.parallel_block and cfg.fp32_residual
+        stream = cfg.fp32_residual and cfg.norm_placement == "pre" and not cfg.post_norm
         if cfg.looped or stream:
             # a span of layers may run several times with the same weights: every layer RUN has its own cache / state
             # (the runtime is told which), and every pass starts by adding the embedding output (not the first) and the

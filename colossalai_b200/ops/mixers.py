@@ -1,6 +1,8 @@
 """Python face of the sequence-mixer kernels (kernel/csrc/mixers.cu): short causal convolution with a carried window,
-recurrent state scans (decayed outer-product state with optional rotary positions, gated delta rule), group RMS norm
-with a sigmoid / silu gate, RMS norm of a sublayer's output added to an fp32 residual stream, sums into the fp32 stream
+recurrent state scans (decayed outer-product state with optional rotary positions, gated delta rule, per-token gated
+outer-product state for selective state spaces and the exponentially gated matrix memory, per-channel gated linear
+recurrence), group RMS norm with a sigmoid / silu gate before or after the norm, rotary positions + unit norm of q / k
+heads, the mean of RMS-normed mixer outputs, RMS norm of a sublayer's output added to an fp32 residual stream, sums into the fp32 stream
 fused with the next RMS / layer norm, rotary positions from an fp32 angle table, the cache rows of latent attention, and
 paged attention with a distance-bucket bias and a softmax sink (values optionally read from the key rows).
 
@@ -24,7 +26,8 @@ from ._dtypes import code
 
 __all__ = ["RaggedMeta", "short_conv_silu", "state_scan_decay", "state_scan_delta", "gated_group_rms_norm",
            "rms_norm_residual", "rms_norm_f32in", "paged_kv_write_mix", "paged_bias_attention", "log_bucket_starts",
-           "bucket_lut", "rotary_table", "rotary_half", "stream_add_norm", "latent_kv_write"]
+           "bucket_lut", "rotary_table", "rotary_half", "stream_add_norm", "latent_kv_write", "state_scan_ssd",
+           "state_scan_mlstm", "lru_scan", "rotary_unit_norm", "sigmoid_gate_mul", "norm_mean"]
 
 _lib = None
 _SPLIT_BELOW_TILES = 148        # attention steps with fewer CTAs than SMs split their keys
@@ -202,18 +205,20 @@ def rotary_half(src: torch.Tensor, dst: torch.Tensor, heads: int, src_head_strid
 
 # ------------------------------------------------------------------------------------------------ short convolution
 def short_conv_silu(x: torch.Tensor, weight: torch.Tensor, state: torch.Tensor, meta: RaggedMeta,
-                    activation: bool = True) -> torch.Tensor:
+                    activation: bool = True, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """x [T, C] (may be a column slice, unit stride inside a row); weight [C, taps], last column = current token;
-    state [slots, taps - 1, C] = the last inputs of every sequence, read and advanced.  Returns silu(conv) [T, C]."""
+    state [slots, taps - 1, C] = the last inputs of every sequence, read and advanced; `bias` [C] is added to the sum of
+    the taps.  Returns silu(conv) (or the plain sum when `activation` is off) [T, C]."""
     T, C = x.shape
     taps = weight.shape[1]
     out = torch.empty(T, C, dtype=x.dtype, device=x.device)
     if use_native(x):
         assert x.stride(1) == 1 and weight.is_contiguous() and state.is_contiguous() and state.dtype == x.dtype
+        assert bias is None or (bias.is_contiguous() and bias.dtype == x.dtype and bias.numel() == C)
         loader.check(_get_lib().cb_short_conv_silu(
-            loader.ptr(x), _i64(x.stride(0)), loader.ptr(weight), loader.ptr(state), loader.ptr(out), _i64(C),
-            loader.ptr(meta.cu_q), loader.ptr(meta.ctx_len), loader.ptr(meta.slots), meta.nseq, meta.max_q, C, taps,
-            int(activation), 1, code(x.dtype), loader.stream_ptr()), "short_conv_silu")
+            loader.ptr(x), _i64(x.stride(0)), loader.ptr(weight), loader.ptr(bias), loader.ptr(state), loader.ptr(out),
+            _i64(C), loader.ptr(meta.cu_q), loader.ptr(meta.ctx_len), loader.ptr(meta.slots), meta.nseq, meta.max_q, C,
+            taps, int(activation), 1, code(x.dtype), loader.stream_ptr()), "short_conv_silu")
         loader.launch_counter.add("short_conv_silu", 2)
         return out
     t0 = 0
@@ -226,6 +231,8 @@ def short_conv_silu(x: torch.Tensor, weight: torch.Tensor, state: torch.Tensor, 
         acc = torch.zeros(n, C)
         for i in range(taps):
             acc += full[i:i + n] * w[:, i]
+        if bias is not None:
+            acc += bias.float()
         out[t0:t0 + n] = (F.silu(acc) if activation else acc).to(x.dtype)
         if taps > 1:
             state[slot] = full[n:].to(state.dtype)
@@ -235,7 +242,8 @@ def short_conv_silu(x: torch.Tensor, weight: torch.Tensor, state: torch.Tensor, 
 
 # ------------------------------------------------------------------------------------------------ state scans
 def _scan_native(mode, q, k, v, araw, braw, head_decay, a_log, dt_bias, state, meta, heads, qk_heads, dim, vdim,
-                 act_silu, unit_qk, unit_eps, q_scale, k_scale=1.0, rot_table=None, rot_dims=0):
+                 act_silu, unit_qk, unit_eps, q_scale, k_scale=1.0, rot_table=None, rot_dims=0, gate_cap=0.0,
+                 gate_kind=0, state_n=None, state_m=None):
     T = q.shape[0]
     out = torch.empty(T, heads * vdim, dtype=torch.float32, device=q.device)
     for t in (q, k, v):
@@ -251,8 +259,9 @@ def _scan_native(mode, q, k, v, araw, braw, head_decay, a_log, dt_bias, state, m
         loader.ptr(out), loader.ptr(work), _i64(T), loader.ptr(meta.cu_q), loader.ptr(meta.ctx_len),
         loader.ptr(meta.slots), meta.nseq, heads, qk_heads, dim, vdim, int(act_silu), int(unit_qk), _f(unit_eps),
         _f(q_scale), _f(k_scale), loader.ptr(rot_table), int(rot_dims if rot_table is not None else 0),
-        loader.ptr(meta.token_pos), code(q.dtype), loader.stream_ptr()), "state_scan")
-    loader.launch_counter.add("state_scan", 2)
+        loader.ptr(meta.token_pos), int(gate_kind), _f(gate_cap), loader.ptr(state_n), loader.ptr(state_m),
+        code(q.dtype), loader.stream_ptr()), "state_scan")
+    loader.launch_counter.add("state_scan", 3 if gate_kind == 2 else 2)
     return out
 
 
@@ -337,13 +346,146 @@ def state_scan_delta(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay_pr
     return out
 
 
+def _softplus(x: torch.Tensor) -> torch.Tensor:
+    return torch.where(x > 20.0, x, torch.log1p(torch.exp(torch.clamp(x, max=20.0))))
+
+
+def state_scan_ssd(c: torch.Tensor, b: torch.Tensor, x: torch.Tensor, dt: torch.Tensor, dt_bias: torch.Tensor,
+                   a_log: torch.Tensor, skip: torch.Tensor, state: torch.Tensor, meta: RaggedMeta, heads: int,
+                   groups: int, dim: int, vdim: int) -> torch.Tensor:
+    """Selective state space, one matrix S [dim, vdim] per head.  Per token and head h (group g = h // (heads / groups)):
+    step = softplus(dt_h + dt_bias_h); S <- exp(-exp(a_log_h) * step) S + step * outer(b_g, x_h); y_h = S^T c_g + skip_h x_h.
+    c, b [T, groups x dim], x [T, heads x vdim], dt [T, heads] (any float dtype; steps, decays and S are fp32);
+    dt_bias, a_log, skip [heads] fp32; state [slots, heads, dim, vdim] fp32.  Returns fp32 y [T, heads x vdim]."""
+    if dim > 256:
+        raise NotImplementedError("state_scan: key width above 256 is not supported")
+    if use_native(x):
+        return _scan_native(2, c, b, x, dt, None, skip, a_log, dt_bias, state, meta, heads, groups, dim, vdim,
+                            False, False, 0.0, 1.0, gate_kind=1)
+    T = x.shape[0]
+    out = torch.empty(T, heads * vdim, dtype=torch.float32)
+    rep = heads // groups
+    A = a_log.float().exp()
+    t0 = 0
+    for n, ctx, slot in zip(meta.q_lens, meta.ctx_lens, meta.slot_list):
+        if n == 0:
+            continue
+        S = state[slot].clone() if ctx > 0 else torch.zeros_like(state[slot])
+        cc = c[t0:t0 + n].float().view(n, groups, dim).repeat_interleave(rep, 1)
+        bb = b[t0:t0 + n].float().view(n, groups, dim).repeat_interleave(rep, 1)
+        xx = x[t0:t0 + n].float().view(n, heads, vdim)
+        step = _softplus(dt[t0:t0 + n].float() + dt_bias.float())
+        dec = torch.exp(-A * step)
+        for t in range(n):
+            S = dec[t][:, None, None] * S + bb[t][:, :, None] * (step[t][:, None] * xx[t])[:, None, :]
+            out[t0 + t] = (torch.einsum("hdv,hd->hv", S, cc[t]) + skip.float()[:, None] * xx[t]).reshape(-1)
+        state[slot] = S
+        t0 += n
+    return out
+
+
+def state_scan_mlstm(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gates: torch.Tensor, gate_bias: torch.Tensor,
+                     gate_cap: float, state: torch.Tensor, state_n: torch.Tensor, state_m: torch.Tensor,
+                     meta: RaggedMeta, heads: int, dim: int, vdim: int, q_scale: float,
+                     den_eps: float = 1e-6) -> torch.Tensor:
+    """Matrix memory with exponential gates.  gates [T, 2 x heads] = pre-activations of the input gate, then of the
+    forget gate; gate_bias [2 x heads] fp32.  With cap(z) = gate_cap * tanh(z / gate_cap) (identity when gate_cap is 0):
+    i = cap(gates_i + bias_i), f = logsigmoid(cap(gates_f + bias_f)); m' = max(f + m, i);
+    S <- exp(f + m - m') S + exp(i - m') outer(k, v), n likewise with k alone, m <- m';
+    y = S^T q / (max(|n . q|, exp(-m)) + den_eps) with q scaled by `q_scale`.  S, n and m start at zero and are carried
+    in fp32 (state [slots, heads, dim, vdim], state_n [slots, heads, dim], state_m [slots, heads]).  Returns fp32 y."""
+    if dim > 256:
+        raise NotImplementedError("state_scan: key width above 256 is not supported")
+    if use_native(q):
+        assert gates.stride(1) == 1 and state_n.is_contiguous() and state_m.is_contiguous()
+        assert abs(den_eps - 1e-6) < 1e-12, "the kernel holds the denominator's floor at 1e-6"
+        return _scan_native(2, q, k, v, gates, None, None, None, gate_bias, state, meta, heads, heads, dim, vdim,
+                            False, False, 0.0, q_scale, gate_cap=gate_cap, gate_kind=2, state_n=state_n,
+                            state_m=state_m)
+    T = q.shape[0]
+    out = torch.empty(T, heads * vdim, dtype=torch.float32)
+    t0 = 0
+    for cnt, ctx, slot in zip(meta.q_lens, meta.ctx_lens, meta.slot_list):
+        if cnt == 0:
+            continue
+        S = state[slot].clone() if ctx > 0 else torch.zeros_like(state[slot])
+        nn_ = state_n[slot].clone() if ctx > 0 else torch.zeros_like(state_n[slot])
+        m = state_m[slot].clone() if ctx > 0 else torch.zeros_like(state_m[slot])
+        qq = q[t0:t0 + cnt].float().view(cnt, heads, dim) * q_scale
+        kk = k[t0:t0 + cnt].float().view(cnt, heads, dim)
+        vv = v[t0:t0 + cnt].float().view(cnt, heads, vdim)
+        z = gates[t0:t0 + cnt].float() + gate_bias.float()
+        if gate_cap:
+            z = gate_cap * torch.tanh(z / gate_cap)
+        ig, fg = z[:, :heads], F.logsigmoid(z[:, heads:])
+        for t in range(cnt):
+            mn = torch.maximum(fg[t] + m, ig[t])
+            a, w = torch.exp(fg[t] + m - mn), torch.exp(ig[t] - mn)
+            S = a[:, None, None] * S + kk[t][:, :, None] * (w[:, None] * vv[t])[:, None, :]
+            nn_ = a[:, None] * nn_ + w[:, None] * kk[t]
+            m = mn
+            den = torch.maximum((nn_ * qq[t]).sum(-1).abs(), torch.exp(-m)) + den_eps
+            out[t0 + t] = (torch.einsum("hdv,hd->hv", S, qq[t]) / den[:, None]).reshape(-1)
+        state[slot], state_n[slot], state_m[slot] = S, nn_, m
+        t0 += cnt
+    return out
+
+
+def _gelu_tanh(z: torch.Tensor) -> torch.Tensor:
+    return 0.5 * z * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (z + 0.044715 * z * z * z)))
+
+
+def lru_scan(u: torch.Tensor, gates: torch.Tensor, gate_bias: torch.Tensor, lam: torch.Tensor, branch: torch.Tensor,
+             state: torch.Tensor, meta: RaggedMeta, c: float = 8.0) -> torch.Tensor:
+    """Gated linear recurrence per channel.  u [T, C]; gates [blocks, T, 2 x C / blocks] fp32 = pre-activations of the
+    recurrence gate, then of the input gate, of every block's channels (without `gate_bias` [blocks, 2 x C / blocks]);
+    lam [C] fp32; branch [T, C] = pre-activation of the multiplicative branch.  Per token:
+    r = sigmoid(.), i = sigmoid(.), log a = -c r softplus(lam), S <- a S + sqrt(1 - a^2) i u, out = S * gelu_tanh(branch).
+    S starts at zero and is carried in fp32 (state [slots, C]).  Returns [T, C] in u's dtype."""
+    T, C = u.shape
+    nb = gates.shape[0]
+    bw = C // nb
+    if use_native(u):
+        assert gates.dtype == torch.float32 and gates.is_contiguous() and u.stride(1) == 1 and branch.stride(1) == 1
+        assert state.dtype == torch.float32 and state.is_contiguous() and branch.dtype == u.dtype
+        out = torch.empty(T, C, dtype=u.dtype, device=u.device)
+        loader.check(_get_lib().cb_lru_scan(
+            loader.ptr(u), _i64(u.stride(0)), loader.ptr(gates), loader.ptr(gate_bias), loader.ptr(lam),
+            loader.ptr(branch), _i64(branch.stride(0)), loader.ptr(state), loader.ptr(out), _i64(T), loader.ptr(meta.cu_q),
+            loader.ptr(meta.ctx_len), loader.ptr(meta.slots), meta.nseq, C, nb, _f(c), code(u.dtype),
+            loader.stream_ptr()), "lru_scan")
+        loader.launch_counter.add("lru_scan")
+        return out
+    out = torch.empty(T, C, dtype=u.dtype)
+    g = (gates.float() + gate_bias.float()[:, None, :]).sigmoid()                 # [blocks, T, 2 bw]
+    r = g[:, :, :bw].permute(1, 0, 2).reshape(T, C)
+    ii = g[:, :, bw:].permute(1, 0, 2).reshape(T, C)
+    loga = -c * r * _softplus(lam.float())
+    a = torch.exp(loga)
+    mult = torch.sqrt(-torch.expm1(2.0 * loga)) * ii * u.float()
+    y = _gelu_tanh(branch.float())
+    t0 = 0
+    for n, ctx, slot in zip(meta.q_lens, meta.ctx_lens, meta.slot_list):
+        if n == 0:
+            continue
+        S = state[slot].clone() if ctx > 0 else torch.zeros_like(state[slot])
+        for t in range(t0, t0 + n):
+            S = a[t] * S + mult[t]
+            out[t] = (S * y[t]).to(u.dtype)
+        state[slot] = S
+        t0 += n
+    return out
+
+
 # ------------------------------------------------------------------------------------------------ norms
 def gated_group_rms_norm(o: torch.Tensor, weight: Optional[torch.Tensor], gate: Optional[torch.Tensor], group: int,
-                         eps: float, out_dtype: torch.dtype, gate_act: str = "sigmoid") -> torch.Tensor:
+                         eps: float, out_dtype: torch.dtype, gate_act: str = "sigmoid",
+                         gate_first: bool = False) -> torch.Tensor:
     """o [T, C] fp32 -> o / sqrt(mean over each group of `group` channels + eps) * weight[c % len(weight)]
-    * act(gate), in `out_dtype`; act is the sigmoid or (`gate_act="silu"`) the silu; without `weight` the norm is plain."""
+    * act(gate), in `out_dtype`; act is the sigmoid or (`gate_act="silu"`) the silu; without `weight` the norm is plain.
+    With `gate_first` the gate multiplies o BEFORE the norm: (o act(gate)) / rms_group(o act(gate)) * weight."""
     T, C = o.shape
-    assert gate_act in ("sigmoid", "silu")
+    assert gate_act in ("sigmoid", "silu") and not (gate_first and gate is None)
     if use_native(o):
         out = torch.empty(T, C, dtype=out_dtype, device=o.device)
         assert o.is_contiguous() and (weight is None or weight.dtype == out_dtype) and \
@@ -351,9 +493,13 @@ def gated_group_rms_norm(o: torch.Tensor, weight: Optional[torch.Tensor], gate: 
         loader.check(_get_lib().cb_gated_group_rmsnorm(
             loader.ptr(o), loader.ptr(weight), 1 if weight is None else weight.numel(), loader.ptr(gate),
             _i64(0 if gate is None else gate.stride(0)), loader.ptr(out), _i64(T), C, group, _f(eps),
-            int(gate_act == "silu"), code(out_dtype), loader.stream_ptr()), "gated_group_rmsnorm")
+            int(gate_act == "silu") | (2 if gate_first else 0), code(out_dtype), loader.stream_ptr()),
+            "gated_group_rmsnorm")
         loader.launch_counter.add("gated_group_rmsnorm")
         return out
+    if gate_first:
+        o = o * (torch.sigmoid(gate.float()) if gate_act == "sigmoid" else F.silu(gate.float()))
+        gate = None
     y = o.view(T, C // group, group)
     y = y / torch.sqrt((y * y).mean(-1, keepdim=True) + eps)
     y = y.reshape(T, C)
@@ -394,6 +540,82 @@ def rms_norm_f32in(x: torch.Tensor, weight: torch.Tensor, eps: float, offset: fl
         return out
     xf = x.float()
     return (xf / torch.sqrt((xf * xf).mean(-1, keepdim=True) + eps) * (offset + weight.float())).to(weight.dtype)
+
+
+def norm_mean(parts: Sequence[torch.Tensor], weights: Sequence[torch.Tensor], eps: float) -> torch.Tensor:
+    """Mean of RMS-normed tensors: (1 / n) sum_i parts[i] / sqrt(mean(parts[i]^2) + eps) * weights[i], every part
+    [T, W] (compute dtype or fp32, unit stride inside a row) normalised over W in fp32.  Returns fp32 [T, W]: the
+    output of mixers that run side by side, ready to be added to an fp32 residual stream."""
+    n = len(parts)
+    T, W = parts[0].shape
+    assert 1 <= n <= 4 and len(weights) == n
+    if use_native(parts[0]):
+        out = torch.empty(T, W, dtype=torch.float32, device=parts[0].device)
+        ps = list(parts) + [None] * (4 - n)
+        ws = list(weights) + [None] * (4 - n)
+        assert all(p.stride(1) == 1 and p.shape == (T, W) for p in parts)
+        assert all(w.is_contiguous() and w.dtype == p.dtype for w, p in zip(weights, parts))
+        args = []
+        for p_, w_ in zip(ps, ws):
+            args += [loader.ptr(p_), _i64(0 if p_ is None else p_.stride(0)), loader.ptr(w_),
+                     code(p_.dtype) if p_ is not None else 0]
+        loader.check(_get_lib().cb_norm_mean(*args, n, loader.ptr(out), _i64(T), W, _f(eps), loader.stream_ptr()),
+                     "norm_mean")
+        loader.launch_counter.add("norm_mean")
+        return out
+    acc = None
+    for p_, w_ in zip(parts, weights):
+        pf = p_.float()
+        y = pf / torch.sqrt((pf * pf).mean(-1, keepdim=True) + eps) * w_.float()
+        acc = y if acc is None else acc + y
+    return acc * (1.0 / n)
+
+
+def sigmoid_gate_mul(o: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
+    """o [T, C] (contiguous) times sigmoid(gate [T, C], unit stride inside a row), in place; the sigmoid in fp32."""
+    T, C = o.shape
+    if use_native(o):
+        assert o.is_contiguous() and gate.stride(1) == 1 and gate.dtype == o.dtype and gate.shape == o.shape
+        loader.check(_get_lib().cb_sigmoid_gate_mul(loader.ptr(o), loader.ptr(gate), _i64(gate.stride(0)), _i64(T), C,
+                                                    code(o.dtype), loader.stream_ptr()), "sigmoid_gate_mul")
+        loader.launch_counter.add("sigmoid_gate_mul")
+        return o
+    o.copy_((o.float() * torch.sigmoid(gate.float())).to(o.dtype))
+    return o
+
+
+def rotary_unit_norm(x: torch.Tensor, heads: int, dim: int, rot_dims: int, interleaved: bool,
+                     table: Optional[torch.Tensor], token_pos: torch.Tensor, unit_eps: Optional[float]) -> None:
+    """In place on the first `heads x dim` columns of x [T, .]: every head's first `rot_dims` channels are turned by the
+    token's position - pairs (2i, 2i + 1) when `interleaved`, else (i, i + rot_dims / 2); `table` = `rotary_table` of
+    `rot_dims` - and then, with `unit_eps`, the head is divided by sqrt(mean of its squares + unit_eps).  fp32
+    arithmetic, one rounding into x's dtype."""
+    T = x.shape[0]
+    if rot_dims == 0 and unit_eps is None:
+        return
+    if use_native(x):
+        assert x.stride(1) == 1 and (rot_dims == 0 or (table.dtype == torch.float32 and table.shape[1] == rot_dims))
+        loader.check(_get_lib().cb_rotary_unit_norm(
+            loader.ptr(x), _i64(x.stride(0)), _i64(T), heads, dim, rot_dims, int(interleaved),
+            loader.ptr(table if rot_dims else None), loader.ptr(token_pos), int(unit_eps is not None),
+            _f(unit_eps or 0.0), code(x.dtype), loader.stream_ptr()), "rotary_unit_norm")
+        loader.launch_counter.add("rotary_unit_norm")
+        return
+    y = x[:, : heads * dim].float().reshape(T, heads, dim)
+    if rot_dims:
+        half = rot_dims // 2
+        cs = table[token_pos.long()]
+        c, sn = cs[:, None, :half], cs[:, None, half:]
+        if interleaved:
+            a, b = y[..., 0:rot_dims:2], y[..., 1:rot_dims:2]
+            rot = torch.stack([a * c - b * sn, b * c + a * sn], -1).reshape(T, heads, rot_dims)
+        else:
+            a, b = y[..., :half], y[..., half:rot_dims]
+            rot = torch.cat([a * c - b * sn, b * c + a * sn], -1)
+        y = torch.cat([rot, y[..., rot_dims:]], -1)
+    if unit_eps is not None:
+        y = y / torch.sqrt((y * y).mean(-1, keepdim=True) + unit_eps)
+    x[:, : heads * dim] = y.reshape(T, heads * dim).to(x.dtype)
 
 
 _NORM_KINDS = {None: 0, "none": 0, "rms": 1, "layer": 2}
@@ -501,8 +723,10 @@ def paged_bias_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
                          meta: RaggedMeta, scale: float, bias_table: Optional[torch.Tensor] = None,
                          bucket_starts: Optional[torch.Tensor] = None, sink: bool = False,
                          lut: Optional[torch.Tensor] = None, tensor_cores: Optional[bool] = None,
-                         vdim: Optional[int] = None) -> torch.Tensor:
-    """Causal attention of every step token over positions 0..pos of its sequence in the paged cache.
+                         vdim: Optional[int] = None, mask_block: int = 0) -> torch.Tensor:
+    """Causal attention of every step token over positions 0..pos of its sequence in the paged cache; with `mask_block`
+    only over the positions of its own block, floor(pos / mask_block) * mask_block .. pos (blocks are counted from the
+    start of the sequence, whatever the step's cut).
     With `vdim` given and `v_cache` the key cache itself, the values are the first `vdim` columns of the key rows (latent
     attention: one row per token serves as key and value).
     q [T, heads x dim]; caches [blocks, block_size, kv_heads, dim | vdim]; bias_table [buckets, heads] fp32 indexed by
@@ -537,6 +761,8 @@ def paged_bias_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
             R = heads // G
             tiles = meta.nseq * G * ((meta.max_q * R + 63) // 64)
             max_len = max(c + n for c, n in zip(meta.ctx_lens, meta.q_lens))
+            if mask_block:
+                max_len = min(max_len, mask_block + 64)       # keys a tile can see: the split is sized for those
             chunk = splits = 0
             part_o = part_ml = None
             if tiles < _SPLIT_BELOW_TILES and max_len >= 256:
@@ -547,12 +773,17 @@ def paged_bias_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
                     part_ml = _workspace("attn_ml", T * heads * splits * 2, q.device)
                 else:
                     chunk = splits = 0
+            if mask_block and splits:
+                max_len = max(c + n for c, n in zip(meta.ctx_lens, meta.q_lens))
+                splits = -(-max_len // chunk)                 # chunks are counted from key 0
+                part_o = _workspace("attn_o", T * heads * splits * vdim, q.device)
+                part_ml = _workspace("attn_ml", T * heads * splits * 2, q.device)
             loader.check(_get_lib().cb_paged_bias_attention_mma(
                 loader.ptr(q), _i64(q.stride(0)), loader.ptr(k_cache), loader.ptr(v_cache), loader.ptr(block_tables),
                 loader.ptr(meta.cu_q), loader.ptr(meta.ctx_len), loader.ptr(meta.token_pos), loader.ptr(bias_table),
                 loader.ptr(lut), 0 if lut is None else lut.numel(), nb, loader.ptr(out), _i64(T), meta.nseq, meta.max_q,
                 heads, G, dim, vdim, ldv, bs, block_tables.shape[1], _f(scale), int(sink), chunk, splits,
-                loader.ptr(part_o), loader.ptr(part_ml), code(q.dtype), loader.stream_ptr()),
+                loader.ptr(part_o), loader.ptr(part_ml), int(mask_block), code(q.dtype), loader.stream_ptr()),
                 "paged_bias_attention_mma")
             loader.launch_counter.add("paged_bias_attention_mma")
             return out
@@ -560,7 +791,7 @@ def paged_bias_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
             loader.ptr(q), _i64(q.stride(0)), loader.ptr(k_cache), loader.ptr(v_cache), loader.ptr(block_tables),
             loader.ptr(meta.token_seq), loader.ptr(meta.token_pos), loader.ptr(bias_table), loader.ptr(bucket_starts), nb,
             loader.ptr(out), _i64(T), heads, G, dim, vdim, ldv, bs, block_tables.shape[1], _f(scale), int(sink),
-            code(q.dtype), loader.stream_ptr()), "paged_bias_attention")
+            int(mask_block), code(q.dtype), loader.stream_ptr()), "paged_bias_attention")
         loader.launch_counter.add("paged_bias_attention")
         return out
     out = torch.empty(T, heads * vdim, dtype=q.dtype)
@@ -580,6 +811,9 @@ def paged_bias_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
             b = torch.bucketize(dist.clamp(min=0), bucket_starts.to(torch.int64), right=True) - 1
             s = s + bias_table.float()[b].permute(2, 0, 1)
         s = s.masked_fill(dist[None] < 0, float("-inf"))
+        if mask_block:
+            same = (torch.arange(c, L)[:, None] // mask_block) == (torch.arange(L)[None, :] // mask_block)
+            s = s.masked_fill(~same[None], float("-inf"))
         if sink:
             s = torch.cat([s, torch.zeros(heads, n, 1)], -1)
         p = torch.softmax(s, -1)[..., :L]
