@@ -114,7 +114,7 @@ class PagedKVRuntime:
 
     def attend_ragged(self, layer_idx: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float,
                       bias_table=None, bucket_starts=None, sink: bool = False, v_other=None,
-                      lam: float = 0.0, lut=None, mask_block: int = 0) -> torch.Tensor:
+                      lam: float = 0.0, lut=None, mask_block: int = 0, wide_weights: bool = False) -> torch.Tensor:
         """Write the step's K / V rows (values optionally blended with `v_other`) into the layer's pages, then attend
         every step token over positions 0..pos of its sequence (with `mask_block`: over the positions of its own block
         of that many positions only).  q [T, H x dim], k [T, G x dim], v [T, G x vdim]."""
@@ -123,7 +123,8 @@ class PagedKVRuntime:
         kc, vc = self.k_caches[self.cache_index(layer_idx)], self.v_caches[self.cache_index(layer_idx)]
         mops.paged_kv_write_mix(k, v, kc, vc, self.block_tables, self.ragged, v_other=v_other, lam=lam)
         return mops.paged_bias_attention(q, kc, vc, self.block_tables, self.ragged, scale, bias_table=bias_table,
-                                         bucket_starts=bucket_starts, sink=sink, lut=lut, mask_block=mask_block)
+                                         bucket_starts=bucket_starts, sink=sink, lut=lut, mask_block=mask_block,
+                                         wide_weights=wide_weights)
 
     @classmethod
     def scratch(cls, cfg, batch: int, seqlen: int, device, dtype, block_size: int = 16) -> "PagedKVRuntime":

@@ -11,11 +11,21 @@
 // Every recurrence runs token by token in fp32 with one fixed order of operations, so the result at a position does not
 // depend on how the prompt was cut or on what else is in the batch.
 //
-//   cb_short_conv_silu      y = silu(causal depthwise conv(x)) over time, window of taps-1 inputs carried per slot
-//   cb_state_scan           (prepare + scan) per head a matrix M [dim, vdim]: either M <- a_h M + outer(k, v) with one
-//                           decay per head, or the gated delta rule M <- diag(r) M; e = w (v - M^T k); M <- M + outer(k, e)
-//                           with a decay per key channel; the read-out y = M^T q follows the write
-//   cb_gated_group_rmsnorm  out = o / rms_group(o) * w * sigmoid(gate) (or silu(gate); w optional)
+//   cb_short_conv_silu      y = silu(causal depthwise conv(x) + bias) over time (activation and bias optional), window
+//                           of taps-1 inputs carried per slot
+//   cb_state_scan           (prepare + scan) per head a matrix M [dim, vdim]: M <- a_h M + outer(k, v) with one decay
+//                           per head; or the gated delta rule M <- diag(r) M; e = w (v - M^T k); M <- M + outer(k, e)
+//                           with a decay per key channel; or M <- g_t M + w_t outer(k, v) with a decay g_t and a write
+//                           strength w_t per token and head (selective state space: from the step size; matrix memory
+//                           with exponential gates: from a running maximum, with a normaliser vector beside M); the
+//                           read-out y = M^T q follows the write
+//   cb_lru_scan             per channel S <- a_t S + sqrt(1 - a_t^2) i_t u_t with gates from fp32 pre-activations
+//   cb_gated_group_rmsnorm  out = o / rms_group(o) * w * sigmoid(gate) (or silu(gate); w optional; gate before or
+//                           after the norm)
+//   cb_rotary_unit_norm     q / k heads in place: rotary positions on a part of the head (half or interleaved pairs),
+//                           then division by the head's root mean square
+//   cb_norm_mean            mean of up to four RMS-normed [T, W] tensors, fp32 out
+//   cb_sigmoid_gate_mul     o *= sigmoid(gate)
 //   cb_stream_add_norm      x(fp32) += sum of up to four [T, W] addends + a [W] row;  h = cast(rms / layer norm of x)
 //   cb_rotary_half          rotate-half rotary positions from an fp32 [positions, dims] cos|sin table, strided in / out
 //   cb_latent_kv_write      latent attention's cache row: [rms_norm(latent) * w | rotated shared key part]
@@ -33,6 +43,10 @@ namespace {
 CB_DEVICE float silu_f(float x) { return x / (1.f + expf(-x)); }
 CB_DEVICE float sigmoid_f(float x) { return 1.f / (1.f + expf(-x)); }
 CB_DEVICE float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+CB_DEVICE float logsigmoid_f(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
+CB_DEVICE float gelu_tanh_f(float z) {
+  return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
 
 // ------------------------------------------------------------------------------------------------ short convolution
 // The convolution's activation is stored in the compute dtype: for 16-bit outputs the hardware exponential and
@@ -45,6 +59,7 @@ constexpr int CONV_TOK_TILE = 32;
 
 template <typename T>
 __global__ void __launch_bounds__(128) short_conv_silu_kernel(const T* __restrict__ x, int64_t ldx, const T* __restrict__ w,
+                                                              const T* __restrict__ bias,
                                                               const T* __restrict__ state, T* __restrict__ out,
                                                               int64_t ldo, const int* __restrict__ cu_q,
                                                               const int* __restrict__ ctx_len,
@@ -69,9 +84,10 @@ __global__ void __launch_bounds__(128) short_conv_silu_kernel(const T* __restric
     }
   }
   const int j1 = min(j0 + CONV_TOK_TILE, qlen);
+  const float bv = bias != nullptr ? to_f32<T>(bias[c]) : 0.f;
   for (int j = j0; j < j1; ++j) {
     const float cur = to_f32<T>(x[(int64_t)(t0 + j) * ldx + c]);
-    float acc = 0.f;
+    float acc = bv;
 #pragma unroll
     for (int i = 0; i < CONV_MAX_TAPS - 1; ++i)
       if (i < taps - 1) acc = fmaf(wt[i], win[i], acc);
@@ -93,7 +109,8 @@ constexpr int CONV_VEC_TAPS = 4;
 
 template <typename T>
 __global__ void __launch_bounds__(128) short_conv_silu_vec_kernel(const T* __restrict__ x, int64_t ldx,
-                                                                  const T* __restrict__ w, const T* __restrict__ state,
+                                                                  const T* __restrict__ w, const T* __restrict__ bias,
+                                                                  const T* __restrict__ state,
                                                                   T* __restrict__ out, int64_t ldo,
                                                                   const int* __restrict__ cu_q,
                                                                   const int* __restrict__ ctx_len,
@@ -107,11 +124,13 @@ __global__ void __launch_bounds__(128) short_conv_silu_vec_kernel(const T* __res
   if (c >= C || j0 >= qlen) return;
   const bool carried = ctx_len[s] > 0;
   const T* st = state + (int64_t)slots[s] * (taps - 1) * C;
-  float wt[CONV_VEC_TAPS][V], win[CONV_VEC_TAPS - 1][V];
+  float wt[CONV_VEC_TAPS][V], win[CONV_VEC_TAPS - 1][V], bv[V];
 #pragma unroll
-  for (int e = 0; e < V; ++e)
+  for (int e = 0; e < V; ++e) {
+    bv[e] = bias != nullptr ? to_f32<T>(bias[c + e]) : 0.f;
 #pragma unroll
     for (int i = 0; i < CONV_VEC_TAPS; ++i) wt[i][e] = i < taps ? to_f32<T>(w[(int64_t)(c + e) * taps + i]) : 0.f;
+  }
 #pragma unroll
   for (int i = 0; i < CONV_VEC_TAPS - 1; ++i) {
     Vec16<T> v;
@@ -131,7 +150,7 @@ __global__ void __launch_bounds__(128) short_conv_silu_vec_kernel(const T* __res
 #pragma unroll
     for (int e = 0; e < V; ++e) {
       const float cur = v.get(e);
-      float acc = 0.f;
+      float acc = bv[e];
 #pragma unroll
       for (int i = 0; i < CONV_VEC_TAPS - 1; ++i)
         if (i < taps - 1) acc = fmaf(wt[i][e], win[i][e], acc);
@@ -178,7 +197,8 @@ __global__ void __launch_bounds__(128) short_conv_state_kernel(const T* __restri
 }
 
 // ------------------------------------------------------------------------------------------------ recurrent state scan
-enum ScanMode : int { SCAN_DECAY = 0, SCAN_DELTA = 1 };
+enum ScanMode : int { SCAN_DECAY = 0, SCAN_DELTA = 1, SCAN_GATED = 2 };
+enum GateKind : int { GATE_STEP = 1, GATE_EXP = 2 };
 constexpr int SCAN_TOK_TILE = 8;
 
 struct ScanParams {
@@ -202,6 +222,15 @@ struct ScanParams {
   const float* rot_table;       // [positions, rot_dims] cos | sin per position, or null: no rotary positions
   int rot_dims;                 // first channels of every q / k head that are rotated (pairs i, i + rot_dims / 2)
   const int* token_pos;         // [T] position of every token in its sequence
+  // gated mode.  GATE_STEP (selective state space): araw [T, lda] holds heads step pre-activations, dt_bias / a_log
+  // [heads]: step = softplus(araw + dt_bias), decay = exp(-exp(a_log) step), write strength = step; head_decay [heads]
+  // (optional) is the skip D of y += D v.  GATE_EXP (matrix memory with exponential gates): araw holds heads input-gate
+  // then heads forget-gate pre-activations, dt_bias [2 heads] their biases, gate_cap the soft cap (0 = none); the running
+  // maximum and the normaliser vector live in state_m [slots, heads] / state_n [slots, heads, dim].
+  int gate_kind;
+  float gate_cap;
+  float* state_n;
+  float* state_m;
 };
 
 // Two kernels.  `scan_prepare_kernel` is elementwise and fully parallel: activations, unit norms, decays and write
@@ -215,6 +244,7 @@ constexpr int SCAN_COLS = 32;          // 128 threads
 
 struct ScanWork {
   float *q, *k, *g, *beta, *v;         // [T, qk_heads, DK] x2, [T, heads, DK], [T, heads], [T, heads, VP]
+  float* gw;                           // gated mode: [T, heads, 4] = decay, write strength, read-out factor, unused
   int DK, VP;
 };
 
@@ -279,6 +309,25 @@ __global__ void __launch_bounds__(128) scan_prepare_kernel(ScanParams p, ScanWor
     for (int h = threadIdx.x; h < p.heads; h += blockDim.x)
       w.beta[t * p.heads + h] = sigmoid_f(to_f32<T>(((const T*)p.braw)[t * p.ldb + h]));
   }
+  if (MODE == SCAN_GATED) {
+    const T* ar = (const T*)p.araw + t * p.lda;
+    for (int h = threadIdx.x; h < p.heads; h += blockDim.x) {
+      float4 o;
+      if (p.gate_kind == GATE_STEP) {
+        const float step = softplus_f(to_f32<T>(ar[h]) + p.dt_bias[h]);
+        o = make_float4(expf(-expf(p.a_log[h]) * step), step, 1.f, 0.f);
+      } else {                                   // log forget gate, log input gate: the gate kernel turns them into
+        float zi = to_f32<T>(ar[h]) + p.dt_bias[h];              // decay and write strength
+        float zf = to_f32<T>(ar[p.heads + h]) + p.dt_bias[p.heads + h];
+        if (p.gate_cap > 0.f) {
+          zi = p.gate_cap * tanhf(zi / p.gate_cap);
+          zf = p.gate_cap * tanhf(zf / p.gate_cap);
+        }
+        o = make_float4(logsigmoid_f(zf), zi, 1.f, 0.f);
+      }
+      *reinterpret_cast<float4*>(w.gw + (t * p.heads + h) * 4) = o;
+    }
+  }
   const T* v = (const T*)p.v + t * p.ldv;
   for (int idx = threadIdx.x; idx < p.heads * w.VP; idx += blockDim.x) {
     const int h = idx / w.VP, c = idx % w.VP;
@@ -286,6 +335,73 @@ __global__ void __launch_bounds__(128) scan_prepare_kernel(ScanParams p, ScanWor
     if (p.act_silu) vv = silu_f(vv);
     w.v[t * p.heads * w.VP + idx] = vv;
   }
+}
+
+// Matrix memory with exponential gates, the scalar side: one warp per (sequence, head) walks the portion's tokens with the
+// running maximum m and the normaliser n (rows spread over the lanes): m' = max(f + m, i); decay = exp(f + m - m'),
+// write = exp(i - m'); n <- decay n + write k; read-out factor = 1 / (max(|n . q|, exp(-m')) + 1e-6).  The three replace
+// (f, i) in the workspace, where the matrix recurrence reads them.  Loads of the next token are issued before the
+// current one's reduction.
+template <int DK>
+__global__ void __launch_bounds__(128) exp_gate_kernel(ScanParams p, ScanWork w, int nseq) {
+  constexpr int NR = DK >= 32 ? DK / 32 : 1;
+  const int lane = threadIdx.x & 31;
+  const int unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (unit >= nseq * p.heads) return;
+  const int s = unit / p.heads, h = unit % p.heads;
+  const int t0 = p.cu_q[s], t1 = p.cu_q[s + 1];
+  if (t0 >= t1) return;
+  const bool carried = p.ctx_len[s] > 0;
+  const int hk = h / (p.heads / p.qk_heads);
+  float* ng = p.state_n + ((int64_t)p.slots[s] * p.heads + h) * p.dim;
+  float* mg = p.state_m + (int64_t)p.slots[s] * p.heads + h;
+  float n[NR], kc[NR], qc[NR];
+#pragma unroll
+  for (int i = 0; i < NR; ++i) {
+    const int r = lane + 32 * i;
+    n[i] = (carried && r < p.dim) ? ng[r] : 0.f;
+    kc[i] = r < DK ? w.k[((int64_t)t0 * p.qk_heads + hk) * DK + r] : 0.f;
+    qc[i] = r < DK ? w.q[((int64_t)t0 * p.qk_heads + hk) * DK + r] : 0.f;
+  }
+  float m = carried ? *mg : 0.f;
+  float4 cur = *reinterpret_cast<const float4*>(w.gw + ((int64_t)t0 * p.heads + h) * 4);
+  for (int64_t t = t0; t < t1; ++t) {
+    float kn[NR], qn[NR];
+    float4 nxt = cur;
+    if (t + 1 < t1) {
+#pragma unroll
+      for (int i = 0; i < NR; ++i) {
+        const int r = lane + 32 * i;
+        kn[i] = r < DK ? w.k[((t + 1) * p.qk_heads + hk) * DK + r] : 0.f;
+        qn[i] = r < DK ? w.q[((t + 1) * p.qk_heads + hk) * DK + r] : 0.f;
+      }
+      nxt = *reinterpret_cast<const float4*>(w.gw + ((t + 1) * p.heads + h) * 4);
+    }
+    const float f = cur.x, ig = cur.y;
+    const float mn = fmaxf(f + m, ig);
+    const float dec = expf(f + m - mn), wr = expf(ig - mn);
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < NR; ++i) {
+      n[i] = fmaf(dec, n[i], wr * kc[i]);
+      dot = fmaf(n[i], qc[i], dot);
+    }
+    dot = warp_sum(dot);
+    m = mn;
+    const float inv = 1.f / (fmaxf(fabsf(dot), expf(-m)) + 1e-6f);
+    if (lane == 0) *reinterpret_cast<float4*>(w.gw + (t * p.heads + h) * 4) = make_float4(dec, wr, inv, 0.f);
+    if (t + 1 < t1) {
+#pragma unroll
+      for (int i = 0; i < NR; ++i) { kc[i] = kn[i]; qc[i] = qn[i]; }
+    }
+    cur = nxt;
+  }
+#pragma unroll
+  for (int i = 0; i < NR; ++i) {
+    const int r = lane + 32 * i;
+    if (r < p.dim) ng[r] = n[i];
+  }
+  if (lane == 0) *mg = m;
 }
 
 template <int DK, int MODE>
@@ -314,6 +430,7 @@ __global__ void __launch_bounds__(128, DK > 128 ? 2 : 4) state_scan_kernel(ScanP
 #pragma unroll
   for (int i = 0; i < RP; ++i) S[i] = (carried && active && r0 + i < dim) ? Sg[(int64_t)(r0 + i) * vdim + j] : 0.f;
   const float hd = MODE == SCAN_DECAY ? p.head_decay[h] : 0.f;
+  const float skip = (MODE == SCAN_GATED && p.head_decay != nullptr) ? p.head_decay[h] : 0.f;
 
   auto load_tile = [&](int stage, int tb) {
     float* base = scan_smem + stage * STAGE;
@@ -334,6 +451,9 @@ __global__ void __launch_bounds__(128, DK > 128 ? 2 : 4) state_scan_kernel(ScanP
     }
     if (MODE == SCAN_DELTA && threadIdx.x < nt)
       sv[SCAN_TOK_TILE * SCAN_COLS + threadIdx.x] = w.beta[(int64_t)(tb + threadIdx.x) * p.heads + h];
+    if (MODE == SCAN_GATED && threadIdx.x < nt)
+      cp_async16f(sv + SCAN_TOK_TILE * SCAN_COLS + threadIdx.x * 4,
+                  w.gw + ((int64_t)(tb + threadIdx.x) * p.heads + h) * 4);
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
 
@@ -359,7 +479,20 @@ __global__ void __launch_bounds__(128, DK > 128 ? 2 : 4) state_scan_kernel(ScanP
       const float* kq = sk + tt * DKP + r0p;
       const float* qq = sq + tt * DKP + r0p;
       float o0 = 0.f, o1 = 0.f;
-      if (MODE == SCAN_DELTA) {
+      float4 gwv = make_float4(0.f, 0.f, 1.f, 0.f);
+      if (MODE == SCAN_GATED) {
+        gwv = *reinterpret_cast<const float4*>(sbeta + tt * 4);
+        const float u = gwv.y * vv;
+#pragma unroll
+        for (int i = 0; i < RP; i += 4) {
+          const float4 k4 = *reinterpret_cast<const float4*>(kq + i);
+          const float4 q4 = *reinterpret_cast<const float4*>(qq + i);
+          S[i] = fmaf(gwv.x, S[i], k4.x * u); S[i + 1] = fmaf(gwv.x, S[i + 1], k4.y * u);
+          S[i + 2] = fmaf(gwv.x, S[i + 2], k4.z * u); S[i + 3] = fmaf(gwv.x, S[i + 3], k4.w * u);
+          o0 = fmaf(S[i], q4.x, o0); o1 = fmaf(S[i + 1], q4.y, o1);
+          o0 = fmaf(S[i + 2], q4.z, o0); o1 = fmaf(S[i + 3], q4.w, o1);
+        }
+      } else if (MODE == SCAN_DELTA) {
         const float* gq = sg + tt * DKP + r0p;
         float a0 = 0.f, a1 = 0.f;
 #pragma unroll
@@ -397,6 +530,7 @@ __global__ void __launch_bounds__(128, DK > 128 ? 2 : 4) state_scan_kernel(ScanP
       float o = o0 + o1;
       o += __shfl_xor_sync(0xffffffffu, o, 1);
       o += __shfl_xor_sync(0xffffffffu, o, 2);
+      if (MODE == SCAN_GATED) o = fmaf(o, gwv.z, skip * vv);
       if (active && part == 0) p.out[t * ((int64_t)p.heads * vdim) + h * vdim + j] = o;
     }
     __syncthreads();                            // this stage may be refilled in the next pass
@@ -438,8 +572,17 @@ int launch_scan(const ScanParams& p, float* work, int64_t tokens, int nseq, cuda
   w.k = w.q + tokens * p.qk_heads * w.DK;
   w.g = w.k + tokens * p.qk_heads * w.DK;
   w.beta = w.g + (MODE == SCAN_DELTA ? tokens * p.heads * w.DK : 0);
-  w.v = w.beta + (MODE == SCAN_DELTA ? (tokens * p.heads + 3) / 4 * 4 : 0);
+  w.gw = w.beta;
+  w.v = w.beta + (MODE == SCAN_DELTA ? (tokens * p.heads + 3) / 4 * 4 : (MODE == SCAN_GATED ? tokens * p.heads * 4 : 0));
   scan_prepare_kernel<MODE, T><<<(unsigned)tokens, 128, 0, st>>>(p, w);
+  if (MODE == SCAN_GATED && p.gate_kind == GATE_EXP) {
+    const unsigned blocks = (unsigned)((nseq * p.heads + 3) / 4);
+    if (w.DK == 16) exp_gate_kernel<16><<<blocks, 128, 0, st>>>(p, w, nseq);
+    else if (w.DK == 32) exp_gate_kernel<32><<<blocks, 128, 0, st>>>(p, w, nseq);
+    else if (w.DK == 64) exp_gate_kernel<64><<<blocks, 128, 0, st>>>(p, w, nseq);
+    else if (w.DK == 128) exp_gate_kernel<128><<<blocks, 128, 0, st>>>(p, w, nseq);
+    else exp_gate_kernel<256><<<blocks, 128, 0, st>>>(p, w, nseq);
+  }
   if (w.DK == 16) return launch_scan_dk<16, MODE>(p, w, nseq, st);
   if (w.DK == 32) return launch_scan_dk<32, MODE>(p, w, nseq, st);
   if (w.DK == 64) return launch_scan_dk<64, MODE>(p, w, nseq, st);
@@ -454,7 +597,9 @@ template <typename T>
 __global__ void __launch_bounds__(256) gated_group_rmsnorm_kernel(const float* __restrict__ o, const T* __restrict__ w,
                                                                   int wn, const T* __restrict__ gate, int64_t ldg,
                                                                   T* __restrict__ out, int64_t tokens, int C, int group,
-                                                                  float eps, int gate_silu) {
+                                                                  float eps, int flags) {
+  const bool gate_silu = flags & 1;
+  const bool gate_first = (flags & 2) && gate != nullptr;      // the gate multiplies o before the norm
   const int lane = threadIdx.x & 31;
   const int64_t unit = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int ngroups = C / group;
@@ -463,14 +608,26 @@ __global__ void __launch_bounds__(256) gated_group_rmsnorm_kernel(const float* _
   const int c0 = (int)(unit % ngroups) * group;
   const float* row = o + t * C + c0;
   float ss = 0.f;
-  for (int i = lane; i < group; i += 32) ss = fmaf(row[i], row[i], ss);
+  for (int i = lane; i < group; i += 32) {
+    float v = row[i];
+    if (gate_first) {
+      const float gv = to_f32<T>(gate[t * ldg + c0 + i]);
+      v *= gate_silu ? silu_f(gv) : sigmoid_f(gv);
+    }
+    ss = fmaf(v, v, ss);
+  }
   ss = warp_sum(ss);
   const float r = 1.f / sqrtf(ss / (float)group + eps);
   for (int i = lane; i < group; i += 32) {
     const int c = c0 + i;
-    float y = row[i] * r;
+    float y = row[i];
+    if (gate_first) {
+      const float gv = to_f32<T>(gate[t * ldg + c]);
+      y *= gate_silu ? silu_f(gv) : sigmoid_f(gv);
+    }
+    y *= r;
     if (w != nullptr) y *= to_f32<T>(w[c % wn]);
-    if (gate != nullptr) {
+    if (gate != nullptr && !gate_first) {
       const float gv = to_f32<T>(gate[t * ldg + c]);
       y *= gate_silu ? silu_f(gv) : sigmoid_f(gv);
     }
@@ -849,7 +1006,7 @@ __global__ void __launch_bounds__(128) paged_bias_attention_kernel(
     const int* __restrict__ block_tables, const int* __restrict__ token_seq, const int* __restrict__ token_pos,
     const float* __restrict__ bias_table, const int* __restrict__ bucket_start, int nbuckets, T* __restrict__ out,
     int64_t tokens, int heads, int kv_heads, int dim, int vdim, int ldv, int block_size, int max_blocks, float scale,
-    int sink) {
+    int sink, int mask_block) {
   extern __shared__ float smem[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   float* qs = smem + warp * dim;
@@ -870,7 +1027,8 @@ __global__ void __launch_bounds__(128) paged_bias_attention_kernel(
   float acc[ATT_MAX_VREG];
 #pragma unroll
   for (int r = 0; r < ATT_MAX_VREG; ++r) acc[r] = 0.f;
-  for (int j0 = 0; j0 <= pos; j0 += 32) {
+  // with a block mask the keys start at the first position of the query's own block
+  for (int j0 = mask_block > 0 ? pos / mask_block * mask_block : 0; j0 <= pos; j0 += 32) {
     const int jk = j0 + lane;
     float sc = -INFINITY;
     int64_t myrow = 0;
@@ -949,6 +1107,16 @@ template <> CB_DEVICE uint32_t pack2<__half>(float lo, float hi) {
   __half2 v = __floats2half2_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
+// what a pair of fp32 values loses when it is packed into 16 bits: the second operand of a two-term product
+template <typename T> CB_DEVICE uint32_t pack2_rest(float lo, float hi, uint32_t packed);
+template <> CB_DEVICE uint32_t pack2_rest<__nv_bfloat16>(float lo, float hi, uint32_t packed) {
+  const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&packed));
+  return pack2<__nv_bfloat16>(lo - f.x, hi - f.y);
+}
+template <> CB_DEVICE uint32_t pack2_rest<__half>(float lo, float hi, uint32_t packed) {
+  const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&packed));
+  return pack2<__half>(lo - f.x, hi - f.y);
+}
 CB_DEVICE float ex2f(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -982,7 +1150,7 @@ __global__ void __launch_bounds__(128, D > 128 ? 1 : (MT == 2 ? 2 : 3)) paged_bi
     const int* __restrict__ block_tables, const int* __restrict__ cu_q, const int* __restrict__ ctx_len,
     const float* __restrict__ bias_table, const uint8_t* __restrict__ lut, int lut_n, int nbuckets, T* __restrict__ out,
     int heads, int kv_heads, int dim, int vdim, int ldv, int block_size, int max_blocks, float scale, int sink, int chunk,
-    int max_splits, float* __restrict__ part_o, float* __restrict__ part_ml) {
+    int max_splits, float* __restrict__ part_o, float* __restrict__ part_ml, int mask_block, int wide_weights) {
   constexpr int BM = 64 * MT;
   constexpr int LDS = D + 8;                    // padded row: 16-byte aligned, conflict-free fragment reads
   constexpr int TILE = MMA_BN * LDS;
@@ -1006,9 +1174,13 @@ __global__ void __launch_bounds__(128, D > 128 ? 1 : (MT == 2 ? 2 : 3)) paged_bi
   if (row0 >= nrows) return;
   const int ctx = ctx_len[s];
   const int last_row = min(nrows - 1, row0 + BM - 1);
-  const int key_lo = chunk > 0 ? split * chunk : 0;
-  const int pos_max = chunk > 0 ? min(ctx + last_row / R, key_lo + chunk - 1) : ctx + last_row / R;
-  if (key_lo > pos_max) return;                 // this chunk lies beyond every row of the tile
+  // block mask: a row at position p sees keys p / mask_block * mask_block .. p; the tile's keys start at its first row's
+  // block (key chunks that end below it are never read: the merge starts at the row's own first chunk)
+  // (rounded down to a key tile, so that tiles keep their place inside a key chunk and never reach into the next one)
+  const int blk_lo = mask_block > 0 ? (ctx + row0 / R) / mask_block * mask_block / MMA_BN * MMA_BN : 0;
+  const int key_lo = max(chunk > 0 ? split * chunk : 0, blk_lo);
+  const int pos_max = chunk > 0 ? min(ctx + last_row / R, split * chunk + chunk - 1) : ctx + last_row / R;
+  if (key_lo > pos_max) return;                 // this chunk lies beyond (or below) every row of the tile
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, gid = lane >> 2, tig = lane & 3;
   for (int i = tid; i < nbuckets * R; i += 128) tab[i] = bias_table[(i / R) * heads + g * R + (i % R)] * LOG2E;
   const int* bt = block_tables + (int64_t)s * max_blocks;
@@ -1040,7 +1212,7 @@ __global__ void __launch_bounds__(128, D > 128 ? 1 : (MT == 2 ? 2 : 3)) paged_bi
   }
   load_tile(0, key_lo);
 
-  int rr[NR], pos[NR], hr[NR];
+  int rr[NR], pos[NR], hr[NR], lo[NR];
   bool valid[NR];
 #pragma unroll
   for (int e = 0; e < NR; ++e) {
@@ -1048,6 +1220,7 @@ __global__ void __launch_bounds__(128, D > 128 ? 1 : (MT == 2 ? 2 : 3)) paged_bi
     valid[e] = rr[e] < nrows;
     hr[e] = valid[e] ? rr[e] % R : 0;
     pos[e] = valid[e] ? ctx + rr[e] / R : -1;
+    lo[e] = (mask_block > 0 && valid[e]) ? pos[e] / mask_block * mask_block : 0;      // first key the row sees
   }
   float o[MT][D / 8][4];
 #pragma unroll
@@ -1069,6 +1242,7 @@ __global__ void __launch_bounds__(128, D > 128 ? 1 : (MT == 2 ? 2 : 3)) paged_bi
   const bool wlive = wrow0 < nrows;
   const int wlo = ctx + min(nrows - 1, wrow0) / R;
   const int whi = wlive ? ctx + min(nrows - 1, wrow0 + 16 * MT - 1) / R : -1;
+  const int wblk = (mask_block > 0 && wlive) ? whi / mask_block * mask_block : 0;     // latest block start among its rows
   const uint32_t q_addr = (uint32_t)__cvta_generic_to_shared(Qs + ((KS ? 0 : warp * 16 * MT) + (lane & 15)) * LDS +
                                                              (lane >> 4) * 8);
 
@@ -1112,7 +1286,7 @@ __global__ void __launch_bounds__(128, D > 128 ? 1 : (MT == 2 ? 2 : 3)) paged_bi
         }
       }
       const int jlast = j0 + koff + NT * 8 - 1;  // last key this warp scores in the tile
-      const bool unmasked = jlast <= wlo;
+      const bool unmasked = jlast <= wlo && j0 + koff >= wblk;
       const bool far = nbuckets == 0 || wlo - jlast >= lut_n;                 // every distance in the last bucket
       float fb[NR];
 #pragma unroll
@@ -1141,7 +1315,7 @@ __global__ void __launch_bounds__(128, D > 128 ? 1 : (MT == 2 ? 2 : 3)) paged_bi
             for (int e = 0; e < 4; ++e) {
               const int r = mt * 2 + (e >> 1), j = j0 + koff + nt * 8 + tig * 2 + (e & 1);
               float sv = -INFINITY;
-              if (j <= pos[r]) {
+              if (j <= pos[r] && j >= lo[r]) {
                 sv = sacc[mt][nt][e] * sc2;
                 if (nbuckets > 0) {
                   const int n = pos[r] - j;
@@ -1191,6 +1365,18 @@ __global__ void __launch_bounds__(128, D > 128 ? 1 : (MT == 2 ? 2 : 3)) paged_bi
           pa[mt][2] = pack2<T>(sacc[mt][2 * kk + 1][0], sacc[mt][2 * kk + 1][1]);
           pa[mt][3] = pack2<T>(sacc[mt][2 * kk + 1][2], sacc[mt][2 * kk + 1][3]);
         }
+        // `wide_weights`: the softmax weights enter P V as a 16-bit value plus the 16-bit rest of its rounding (two MMAs
+        // per fragment), so a weight keeps about 16 bits of mantissa instead of 8
+        uint32_t pr[MT][4];
+        if (wide_weights) {
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            pr[mt][0] = pack2_rest<T>(sacc[mt][2 * kk][0], sacc[mt][2 * kk][1], pa[mt][0]);
+            pr[mt][1] = pack2_rest<T>(sacc[mt][2 * kk][2], sacc[mt][2 * kk][3], pa[mt][1]);
+            pr[mt][2] = pack2_rest<T>(sacc[mt][2 * kk + 1][0], sacc[mt][2 * kk + 1][1], pa[mt][2]);
+            pr[mt][3] = pack2_rest<T>(sacc[mt][2 * kk + 1][2], sacc[mt][2 * kk + 1][3], pa[mt][3]);
+          }
+        }
         const uint32_t vrow = (uint32_t)__cvta_generic_to_shared(Vs + (koff + kk * 16 + (lane & 15)) * LDS);
 #pragma unroll
         for (int nv = 0; nv < D / 8; ++nv) {
@@ -1199,6 +1385,10 @@ __global__ void __launch_bounds__(128, D > 128 ? 1 : (MT == 2 ? 2 : 3)) paged_bi
                        : "=r"(b0), "=r"(b1) : "r"(vrow + nv * 16));
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt) mma_16816<T>(o[mt][nv], pa[mt], b0, b1);
+          if (wide_weights) {
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) mma_16816<T>(o[mt][nv], pr[mt], b0, b1);
+          }
         }
       }
     }
@@ -1290,25 +1480,27 @@ __global__ void __launch_bounds__(128) attention_merge_kernel(const float* __res
                                                               const float* __restrict__ part_ml,
                                                               const int* __restrict__ token_pos, T* __restrict__ out,
                                                               int64_t tokens, int heads, int vdim, int chunk,
-                                                              int max_splits, int sink) {
+                                                              int max_splits, int sink, int mask_block) {
   const int lane = threadIdx.x & 31;
   const int cblocks = (vdim + 31) >> 5;
   const int64_t item = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (item >= tokens * heads * cblocks) return;
   const int64_t unit = item / cblocks;
   const int c = (int)(item % cblocks) * 32 + lane;
-  const int nsp = token_pos[unit / heads] / chunk + 1;
+  const int tpos = token_pos[unit / heads];
+  const int nsp = tpos / chunk + 1;
+  const int sp0 = mask_block > 0 ? (tpos / mask_block * mask_block) / chunk : 0;      // first chunk with a visible key
   const float* ml = part_ml + unit * max_splits * 2;
   float mm = sink ? 0.f : -INFINITY;
-  for (int sp = lane; sp < nsp; sp += 32) mm = fmaxf(mm, ml[sp * 2]);
+  for (int sp = sp0 + lane; sp < nsp; sp += 32) mm = fmaxf(mm, ml[sp * 2]);
   mm = warp_max(mm);
   const float mu = mm == -INFINITY ? 0.f : mm;
   float l = 0.f;
-  for (int sp = lane; sp < nsp; sp += 32) l = fmaf(ml[sp * 2 + 1], ex2f(ml[sp * 2] - mu), l);
+  for (int sp = sp0 + lane; sp < nsp; sp += 32) l = fmaf(ml[sp * 2 + 1], ex2f(ml[sp * 2] - mu), l);
   l = warp_sum(l) + (sink ? ex2f(0.f - mu) : 0.f);
   float acc = 0.f;
   const float* po = part_o + unit * max_splits * vdim;
-  for (int s0 = 0; s0 < nsp; s0 += 32) {
+  for (int s0 = sp0; s0 < nsp; s0 += 32) {
     const float wl = s0 + lane < nsp ? ex2f(ml[(s0 + lane) * 2] - mu) : 0.f;      // weight of chunk s0 + lane
     const int n = min(32, nsp - s0);
 #pragma unroll 8
@@ -1326,7 +1518,8 @@ int launch_attention_mma(const void* q, int64_t ldq, const void* k_cache, const 
                          const int* cu_q, const int* ctx_len, const int* token_pos, const float* bias_table,
                          const uint8_t* lut, int lut_n, int nbuckets, void* out, int64_t tokens, int nseq, int max_q,
                          int heads, int kv_heads, int dim, int vdim, int ldv, int block_size, int max_blocks, float scale,
-                         int sink, int chunk, int max_splits, float* part_o, float* part_ml, cudaStream_t st) {
+                         int sink, int chunk, int max_splits, float* part_o, float* part_ml, int mask_block,
+                         int wide_weights, cudaStream_t st) {
   const int R = heads / kv_heads;
   constexpr int BM = 64 * MT;
   const bool kv_same = v_cache == k_cache && ldv == dim;
@@ -1343,13 +1536,191 @@ int launch_attention_mma(const void* q, int64_t ldq, const void* k_cache, const 
   dim3 grid(rowtiles * (chunk > 0 ? max_splits : 1), kv_heads, nseq);
   kern<<<grid, 128, smem, st>>>((const T*)q, ldq, (const T*)k_cache, (const T*)v_cache, block_tables, cu_q, ctx_len,
                                 bias_table, lut, lut_n, nbuckets, (T*)out, heads, kv_heads, dim, vdim, ldv, block_size,
-                                max_blocks, scale, sink, chunk, max_splits, part_o, part_ml);
+                                max_blocks, scale, sink, chunk, max_splits, part_o, part_ml, mask_block, wide_weights);
   if (chunk > 0) {
     const int64_t units = tokens * heads * ((vdim + 31) / 32);
     attention_merge_kernel<T><<<(unsigned)((units + 3) / 4), 128, 0, st>>>(part_o, part_ml, token_pos, (T*)out, tokens,
-                                                                          heads, vdim, chunk, max_splits, sink);
+                                                                          heads, vdim, chunk, max_splits, sink, mask_block);
   }
   return CB_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------------------------------------ gated linear recurrence
+// One thread per (sequence, channel): S <- a_t S + sqrt(1 - a_t^2) i_t u_t over the portion's tokens, out = S gelu_tanh(y).
+// r = sigmoid(gate_r + bias), i = sigmoid(gate_i + bias), log a = -c r softplus(lam); 1 - a^2 = -expm1(2 log a) keeps its
+// digits when a is close to one.  gates [blocks, T, 2 bw] fp32: channel j of block b at [b][t][j] (recurrence gate) and
+// [b][t][bw + j] (input gate).  Everything that does not depend on S - loads, gates, the branch - is done for LRU_UNROLL
+// tokens at once, so their loads are in flight together; the chain through S is one FMA per token.
+constexpr int LRU_UNROLL = 8;
+
+template <typename T>
+__global__ void __launch_bounds__(128) lru_scan_kernel(const T* __restrict__ u, int64_t ldu, const float* __restrict__ gates,
+                                                       const float* __restrict__ gbias, const float* __restrict__ lam,
+                                                       const T* __restrict__ branch, int64_t ldb, float* __restrict__ state,
+                                                       T* __restrict__ out, int64_t tokens, const int* __restrict__ cu_q,
+                                                       const int* __restrict__ ctx_len, const int* __restrict__ slots,
+                                                       int C, int nb, float cmul) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int s = blockIdx.y;
+  const int t0 = cu_q[s], t1 = cu_q[s + 1];
+  if (c >= C || t0 >= t1) return;
+  const int bw = C / nb, b = c / bw, j = c % bw;
+  const float br = gbias[(int64_t)b * 2 * bw + j], bi = gbias[(int64_t)b * 2 * bw + bw + j];
+  const float cl = -cmul * softplus_f(lam[c]);
+  float* Sg = state + (int64_t)slots[s] * C + c;
+  float S = ctx_len[s] > 0 ? *Sg : 0.f;
+  const float* gp = gates + (int64_t)b * tokens * 2 * bw + j;
+  for (int tb = t0; tb < t1; tb += LRU_UNROLL) {
+    float gr[LRU_UNROLL], gi[LRU_UNROLL], uu[LRU_UNROLL], yy[LRU_UNROLL];
+#pragma unroll
+    for (int e = 0; e < LRU_UNROLL; ++e) {
+      const int64_t t = min(tb + e, t1 - 1);
+      gr[e] = gp[t * 2 * bw];
+      gi[e] = gp[t * 2 * bw + bw];
+      uu[e] = to_f32<T>(u[t * ldu + c]);
+      yy[e] = to_f32<T>(branch[t * ldb + c]);
+    }
+    float a[LRU_UNROLL], x[LRU_UNROLL];
+#pragma unroll
+    for (int e = 0; e < LRU_UNROLL; ++e) {
+      const float la = cl * sigmoid_f(gr[e] + br);
+      a[e] = expf(la);
+      x[e] = sqrtf(-expm1f(2.f * la)) * sigmoid_f(gi[e] + bi) * uu[e];
+      yy[e] = gelu_tanh_f(yy[e]);
+    }
+#pragma unroll
+    for (int e = 0; e < LRU_UNROLL; ++e) {
+      if (tb + e < t1) {
+        S = fmaf(a[e], S, x[e]);
+        out[(int64_t)(tb + e) * C + c] = from_f32<T>(S * yy[e]);
+      }
+    }
+  }
+  *Sg = S;
+}
+
+// ------------------------------------------------------------------------------------------------ rotary + unit norm
+// One warp per (token, head), in place: the head's first rot_dims channels are turned by the token's position (table row
+// = cos | sin of rot_dims / 2 angles; pairs (2i, 2i + 1) when interleaved, else (i, i + rot_dims / 2)), then, with
+// `unit`, the whole head is divided by sqrt(mean of squares + eps).  The head sits in shared memory while it is turned.
+constexpr int ROT_MAX_REG = 16;        // head width up to 512
+
+template <typename T>
+__global__ void __launch_bounds__(128) rotary_unit_norm_kernel(T* __restrict__ x, int64_t ldx, int64_t tokens, int heads,
+                                                               int dim, int rot_dims, int interleaved,
+                                                               const float* __restrict__ table,
+                                                               const int* __restrict__ token_pos, int unit, float eps) {
+  extern __shared__ float rot_smem[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t item = (int64_t)blockIdx.x * (blockDim.x >> 5) + warp;
+  if (item >= tokens * heads) return;
+  const int64_t t = item / heads;
+  const int h = (int)(item % heads);
+  T* row = x + t * ldx + (int64_t)h * dim;
+  float* sm = rot_smem + warp * dim;
+  for (int i = lane; i < dim; i += 32) sm[i] = to_f32<T>(row[i]);
+  __syncwarp();
+  const int half = rot_dims >> 1;
+  const float* cs = rot_dims > 0 ? table + (int64_t)token_pos[t] * rot_dims : nullptr;
+  float y[ROT_MAX_REG];
+  float ss = 0.f;
+#pragma unroll
+  for (int e = 0; e < ROT_MAX_REG; ++e) {
+    const int c = lane + 32 * e;
+    y[e] = 0.f;
+    if (c < dim) {
+      float v = sm[c];
+      if (c < rot_dims) {
+        if (interleaved) {
+          const float cc = cs[c >> 1], sn = cs[half + (c >> 1)];
+          v = (c & 1) ? sm[c] * cc + sm[c - 1] * sn : sm[c] * cc - sm[c + 1] * sn;
+        } else if (c < half) {
+          v = sm[c] * cs[c] - sm[c + half] * cs[half + c];
+        } else {
+          v = sm[c] * cs[c - half] + sm[c - half] * cs[c];
+        }
+      }
+      y[e] = v;
+      ss = fmaf(v, v, ss);
+    }
+  }
+  float r = 1.f;
+  if (unit) r = 1.f / sqrtf(warp_sum(ss) / (float)dim + eps);
+#pragma unroll
+  for (int e = 0; e < ROT_MAX_REG; ++e) {
+    const int c = lane + 32 * e;
+    if (c < dim) row[c] = from_f32<T>(y[e] * r);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ mean of normed outputs
+// One CTA per token row: out = (1 / n) sum_j p_j / sqrt(mean(p_j^2) + eps) * w_j over up to four [T, W] tensors (each the
+// 16-bit type T or fp32, its weight of the same type), fp32 out.
+struct NormMeanArgs {
+  const void* p[4];
+  const void* w[4];
+  int64_t ld[4];
+  bool f32[4];
+  int n;
+};
+
+template <typename T, int VEC>
+__global__ void __launch_bounds__(256) norm_mean_kernel(NormMeanArgs g, float* __restrict__ out, int W, float eps) {
+  __shared__ float red[4 * 32];
+  const int64_t t = blockIdx.x;
+  float ss[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    if (j < g.n) {
+      for (int i = threadIdx.x * VEC; i < W; i += blockDim.x * VEC) {
+        float v[VEC];
+        load_vec<T, VEC>(g.p[j], g.f32[j], t * g.ld[j] + i, v);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) ss[j] = fmaf(v[e], v[e], ss[j]);
+      }
+    }
+  }
+  block_sum<4>(ss, red);
+  float r[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) r[j] = 1.f / sqrtf(ss[j] / (float)W + eps);
+  const float inv_n = 1.f / (float)g.n;
+  for (int i = threadIdx.x * VEC; i < W; i += blockDim.x * VEC) {
+    float acc[VEC];
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) acc[e] = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (j < g.n) {
+        float v[VEC], wv[VEC];
+        load_vec<T, VEC>(g.p[j], g.f32[j], t * g.ld[j] + i, v);
+        load_vec<T, VEC>(g.w[j], g.f32[j], i, wv);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) acc[e] += v[e] * r[j] * wv[e];
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) acc[e] *= inv_n;
+    store_vec<T, VEC>(out, true, t * W + i, acc);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ sigmoid gate
+template <typename T, int VEC>
+__global__ void __launch_bounds__(256) sigmoid_gate_mul_kernel(T* __restrict__ o, const T* __restrict__ gate, int64_t ldg,
+                                                               int64_t tokens, int C) {
+  const int per = C / VEC;
+  const int64_t total = tokens * per;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t t = idx / per;
+    const int c = (int)(idx % per) * VEC;
+    float ov[VEC], gv[VEC];
+    load_vec<T, VEC>(o, false, t * C + c, ov);
+    load_vec<T, VEC>(gate, false, t * ldg + c, gv);
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) ov[e] *= sigmoid_f(gv[e]);
+    store_vec<T, VEC>(o, false, t * C + c, ov);
+  }
 }
 
 }  // namespace
@@ -1357,7 +1728,8 @@ int launch_attention_mma(const void* q, int64_t ldq, const void* k_cache, const 
 // ================================================================================================ C launchers
 extern "C" {
 
-int cb_short_conv_silu(const void* x, int64_t ldx, const void* w, void* state, void* out, int64_t ldo, const int* cu_q,
+int cb_short_conv_silu(const void* x, int64_t ldx, const void* w, const void* bias, void* state, void* out, int64_t ldo,
+                       const int* cu_q,
                        const int* ctx_len, const int* slots, int nseq, int max_q, int C, int taps, int apply_silu,
                        int update_state, int dtype, cudaStream_t st) {
   if (taps < 1 || taps > CONV_MAX_TAPS) return (int)cudaErrorInvalidValue;
@@ -1369,11 +1741,11 @@ int cb_short_conv_silu(const void* x, int64_t ldx, const void* w, void* state, v
                      ((uintptr_t)out % 16) == 0 && ((uintptr_t)state % 16) == 0;
     if (vec) {
       dim3 vgrid((C / V + 127) / 128, grid.y, grid.z);
-      short_conv_silu_vec_kernel<T><<<vgrid, 128, 0, st>>>((const T*)x, ldx, (const T*)w, (const T*)state, (T*)out, ldo,
-                                                          cu_q, ctx_len, slots, C, taps, apply_silu);
+      short_conv_silu_vec_kernel<T><<<vgrid, 128, 0, st>>>((const T*)x, ldx, (const T*)w, (const T*)bias, (const T*)state,
+                                                          (T*)out, ldo, cu_q, ctx_len, slots, C, taps, apply_silu);
     } else {
-      short_conv_silu_kernel<T><<<grid, 128, 0, st>>>((const T*)x, ldx, (const T*)w, (const T*)state, (T*)out, ldo, cu_q,
-                                                      ctx_len, slots, C, taps, apply_silu);
+      short_conv_silu_kernel<T><<<grid, 128, 0, st>>>((const T*)x, ldx, (const T*)w, (const T*)bias, (const T*)state,
+                                                      (T*)out, ldo, cu_q, ctx_len, slots, C, taps, apply_silu);
     }
     if (update_state && taps > 1)
       short_conv_state_kernel<T><<<dim3((C + 127) / 128, nseq), 128, 0, st>>>((const T*)x, ldx, (T*)state, cu_q, ctx_len,
@@ -1387,6 +1759,7 @@ int64_t cb_state_scan_workspace(int mode, int64_t tokens, int heads, int qk_head
   const int64_t DK = scan_dk(dim), VP = scan_vp(vdim);
   int64_t n = 2 * tokens * qk_heads * DK + tokens * heads * VP;
   if (mode == SCAN_DELTA) n += tokens * heads * DK + (tokens * heads + 3) / 4 * 4;
+  if (mode == SCAN_GATED) n += tokens * heads * 4;
   return n;
 }
 
@@ -1395,12 +1768,19 @@ int cb_state_scan(int mode, const void* q, int64_t ldq, const void* k, int64_t l
                   const float* a_log, const float* dt_bias, float* state, float* out, float* work, int64_t tokens,
                   const int* cu_q, const int* ctx_len, const int* slots, int nseq, int heads, int qk_heads, int dim,
                   int vdim, int act_silu, int unit_qk, float unit_eps, float q_scale, float k_scale,
-                  const float* rot_table, int rot_dims, const int* token_pos, int dtype, cudaStream_t st) {
+                  const float* rot_table, int rot_dims, const int* token_pos, int gate_kind, float gate_cap,
+                  float* state_n, float* state_m, int dtype, cudaStream_t st) {
   if (nseq == 0 || tokens == 0) return 0;
   if (heads % qk_heads != 0 || rot_dims > dim || (rot_dims & 1)) return (int)cudaErrorInvalidValue;
+  if (mode == SCAN_GATED && ((gate_kind != GATE_STEP && gate_kind != GATE_EXP) || araw == nullptr || dt_bias == nullptr ||
+                             (gate_kind == GATE_STEP && a_log == nullptr) ||
+                             (gate_kind == GATE_EXP && (state_n == nullptr || state_m == nullptr))))
+    return (int)cudaErrorInvalidValue;
   ScanParams p{q, k, v, ldq, ldk, ldv, araw, lda, braw, ldb, head_decay, a_log, dt_bias, state, out, cu_q, ctx_len, slots,
-               heads, qk_heads, dim, vdim, act_silu, unit_qk, unit_eps, q_scale, k_scale, rot_table, rot_dims, token_pos};
+               heads, qk_heads, dim, vdim, act_silu, unit_qk, unit_eps, q_scale, k_scale, rot_table, rot_dims, token_pos,
+               gate_kind, gate_cap, state_n, state_m};
   CB_DISPATCH_FLOAT(dtype, T, {
+    if (mode == SCAN_GATED) return launch_scan<SCAN_GATED, T>(p, work, tokens, nseq, st);
     if (mode == SCAN_DELTA) return launch_scan<SCAN_DELTA, T>(p, work, tokens, nseq, st);
     return launch_scan<SCAN_DECAY, T>(p, work, tokens, nseq, st);
   });
@@ -1575,7 +1955,8 @@ int cb_paged_kv_write_mix(const void* k, int64_t ldk, const void* v, int64_t ldv
 int cb_paged_bias_attention(const void* q, int64_t ldq, const void* k_cache, const void* v_cache, const int* block_tables,
                             const int* token_seq, const int* token_pos, const float* bias_table, const int* bucket_start,
                             int nbuckets, void* out, int64_t tokens, int heads, int kv_heads, int dim, int vdim, int ldv,
-                            int block_size, int max_blocks, float scale, int sink, int dtype, cudaStream_t st) {
+                            int block_size, int max_blocks, float scale, int sink, int mask_block, int dtype,
+                            cudaStream_t st) {
   if (tokens == 0) return 0;
   if (vdim > 32 * ATT_MAX_VREG || heads % kv_heads != 0) return (int)cudaErrorInvalidValue;
   const int nwarps = 4;
@@ -1584,7 +1965,8 @@ int cb_paged_bias_attention(const void* q, int64_t ldq, const void* k_cache, con
   CB_DISPATCH_FLOAT(dtype, T, {
     paged_bias_attention_kernel<T><<<(unsigned)((units + nwarps - 1) / nwarps), nwarps * 32, smem, st>>>(
         (const T*)q, ldq, (const T*)k_cache, (const T*)v_cache, block_tables, token_seq, token_pos, bias_table,
-        bucket_start, nbuckets, (T*)out, tokens, heads, kv_heads, dim, vdim, ldv, block_size, max_blocks, scale, sink);
+        bucket_start, nbuckets, (T*)out, tokens, heads, kv_heads, dim, vdim, ldv, block_size, max_blocks, scale, sink,
+        mask_block);
   });
   return CB_LAUNCH_CHECK();
 }
@@ -1596,7 +1978,8 @@ int cb_paged_bias_attention_mma(const void* q, int64_t ldq, const void* k_cache,
                                 const float* bias_table, const uint8_t* lut, int lut_n, int nbuckets, void* out,
                                 int64_t tokens, int nseq, int max_q, int heads, int kv_heads, int dim, int vdim, int ldv,
                                 int block_size, int max_blocks, float scale, int sink, int chunk, int max_splits,
-                                float* part_o, float* part_ml, int dtype, cudaStream_t st) {
+                                float* part_o, float* part_ml, int mask_block, int wide_weights, int dtype,
+                                cudaStream_t st) {
   if (nseq == 0 || max_q == 0) return 0;
   if (heads % kv_heads != 0 || dim % 8 != 0 || vdim % 8 != 0 || dim > 256 || vdim > 256 || (ldq & 7) || ((uintptr_t)q & 15) ||
       (ldv & 7) || ldv < vdim ||
@@ -1610,15 +1993,16 @@ int cb_paged_bias_attention_mma(const void* q, int64_t ldq, const void* k_cache,
     return launch_attention_mma<T, D, 1, true>(q, ldq, k_cache, v_cache, block_tables, cu_q, ctx_len, token_pos,       \
                                                bias_table, lut, lut_n, nbuckets, out, tokens, nseq, max_q, heads,      \
                                                kv_heads, dim, vdim, ldv, block_size, max_blocks, scale, sink, chunk,   \
-                                               max_splits, part_o, part_ml, st);                                       \
+                                               max_splits, part_o, part_ml, mask_block, wide_weights, st);             \
   if (wide)                                                                                                           \
     return launch_attention_mma<T, D, 2>(q, ldq, k_cache, v_cache, block_tables, cu_q, ctx_len, token_pos, bias_table, \
                                          lut, lut_n, nbuckets, out, tokens, nseq, max_q, heads, kv_heads, dim, vdim,  \
                                          ldv, block_size, max_blocks, scale, sink, chunk, max_splits, part_o, part_ml, \
-                                         st);                                                                         \
+                                         mask_block, wide_weights, st);                                               \
   return launch_attention_mma<T, D, 1>(q, ldq, k_cache, v_cache, block_tables, cu_q, ctx_len, token_pos, bias_table,  \
                                        lut, lut_n, nbuckets, out, tokens, nseq, max_q, heads, kv_heads, dim, vdim,   \
-                                       ldv, block_size, max_blocks, scale, sink, chunk, max_splits, part_o, part_ml, st)
+                                       ldv, block_size, max_blocks, scale, sink, chunk, max_splits, part_o, part_ml,  \
+                                       mask_block, wide_weights, st)
   CB_DISPATCH_HALF(dtype, T, {
     if (dmax <= 32) { CB_ATT_MMA(T, 32); }
     else if (dmax <= 64) { CB_ATT_MMA(T, 64); }
@@ -1629,10 +2013,81 @@ int cb_paged_bias_attention_mma(const void* q, int64_t ldq, const void* k_cache,
       return launch_attention_mma<T, 256, 1>(q, ldq, k_cache, v_cache, block_tables, cu_q, ctx_len, token_pos, bias_table,
                                              lut, lut_n, nbuckets, out, tokens, nseq, max_q, heads, kv_heads, dim, vdim,
                                              ldv, block_size, max_blocks, scale, sink, chunk, max_splits, part_o, part_ml,
-                                             st);
+                                             mask_block, wide_weights, st);
     }
   });
 #undef CB_ATT_MMA
+  return CB_LAUNCH_CHECK();
+}
+
+int cb_lru_scan(const void* u, int64_t ldu, const float* gates, const float* gbias, const float* lam, const void* branch,
+                int64_t ldb, float* state, void* out, int64_t tokens, const int* cu_q, const int* ctx_len, const int* slots,
+                int nseq, int C, int nb, float cmul, int dtype, cudaStream_t st) {
+  if (nseq == 0 || tokens == 0) return 0;
+  if (nb <= 0 || C % nb != 0) return (int)cudaErrorInvalidValue;
+  dim3 grid((C + 127) / 128, nseq);
+  CB_DISPATCH_FLOAT(dtype, T, {
+    lru_scan_kernel<T><<<grid, 128, 0, st>>>((const T*)u, ldu, gates, gbias, lam, (const T*)branch, ldb, state, (T*)out,
+                                             tokens, cu_q, ctx_len, slots, C, nb, cmul);
+  });
+  return CB_LAUNCH_CHECK();
+}
+
+int cb_rotary_unit_norm(void* x, int64_t ldx, int64_t tokens, int heads, int dim, int rot_dims, int interleaved,
+                        const float* table, const int* token_pos, int unit, float eps, int dtype, cudaStream_t st) {
+  if (tokens == 0 || heads == 0) return 0;
+  if (dim > 32 * ROT_MAX_REG || rot_dims > dim || (rot_dims & 1) || (rot_dims > 0 && table == nullptr))
+    return (int)cudaErrorInvalidValue;
+  const int64_t items = tokens * heads;
+  CB_DISPATCH_FLOAT(dtype, T, {
+    rotary_unit_norm_kernel<T><<<(unsigned)((items + 3) / 4), 128, (size_t)4 * dim * sizeof(float), st>>>(
+        (T*)x, ldx, tokens, heads, dim, rot_dims, interleaved, table, token_pos, unit, eps);
+  });
+  return CB_LAUNCH_CHECK();
+}
+
+int cb_norm_mean(const void* p0, int64_t ld0, const void* w0, int dt0, const void* p1, int64_t ld1, const void* w1, int dt1,
+                 const void* p2, int64_t ld2, const void* w2, int dt2, const void* p3, int64_t ld3, const void* w3, int dt3,
+                 int n, float* out, int64_t tokens, int W, float eps, cudaStream_t st) {
+  if (tokens == 0) return 0;
+  if (n < 1 || n > 4) return (int)cudaErrorInvalidValue;
+  NormMeanArgs g;
+  const void* ps[4] = {p0, p1, p2, p3};
+  const void* ws[4] = {w0, w1, w2, w3};
+  const int64_t lds[4] = {ld0, ld1, ld2, ld3};
+  const int dts[4] = {dt0, dt1, dt2, dt3};
+  int half_type = CB_F32;
+  bool vec = W % 4 == 0 && ((uintptr_t)out & 15) == 0;
+  for (int j = 0; j < 4; ++j) {
+    g.p[j] = ps[j]; g.w[j] = ws[j]; g.ld[j] = lds[j]; g.f32[j] = dts[j] == CB_F32;
+    if (j >= n) continue;
+    if (ps[j] == nullptr || ws[j] == nullptr) return (int)cudaErrorInvalidValue;
+    if (dts[j] != CB_F32) {
+      if (half_type != CB_F32 && half_type != dts[j]) return (int)cudaErrorInvalidValue;
+      half_type = dts[j];
+    }
+    const size_t es = dts[j] == CB_F32 ? 4 : 2;
+    vec = vec && lds[j] % 4 == 0 && ((uintptr_t)ps[j] % (4 * es)) == 0 && ((uintptr_t)ws[j] % (4 * es)) == 0;
+  }
+  g.n = n;
+  if (half_type == CB_F32) half_type = CB_BF16;      // no 16-bit operand: the type only names the unused branch
+  CB_DISPATCH_HALF(half_type, T, {
+    if (vec) norm_mean_kernel<T, 4><<<(unsigned)tokens, 256, 0, st>>>(g, out, W, eps);
+    else norm_mean_kernel<T, 1><<<(unsigned)tokens, 256, 0, st>>>(g, out, W, eps);
+  });
+  return CB_LAUNCH_CHECK();
+}
+
+int cb_sigmoid_gate_mul(void* o, const void* gate, int64_t ldg, int64_t tokens, int C, int dtype, cudaStream_t st) {
+  if (tokens == 0 || C == 0) return 0;
+  CB_DISPATCH_FLOAT(dtype, T, {
+    constexpr int V = 16 / sizeof(T);
+    const bool vec = C % V == 0 && ldg % V == 0 && ((uintptr_t)o & 15) == 0 && ((uintptr_t)gate & 15) == 0;
+    const int64_t total = tokens * (vec ? C / V : C);
+    const unsigned grid = (unsigned)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    if (vec) sigmoid_gate_mul_kernel<T, V><<<grid, 256, 0, st>>>((T*)o, (const T*)gate, ldg, tokens, C);
+    else sigmoid_gate_mul_kernel<T, 1><<<grid, 256, 0, st>>>((T*)o, (const T*)gate, ldg, tokens, C);
+  });
   return CB_LAUNCH_CHECK();
 }
 

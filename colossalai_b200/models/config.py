@@ -91,6 +91,7 @@ class MixerSpec:
     head_unit_norm: bool = False      # q, k / rms over the head (after the rotation), no weight
     mask_block: int = 0               # > 0: keys of the query's own block of this many positions only
     out_gate: bool = False            # heads * sigmoid(W_g x) in front of the output projection
+    wide_weights: bool = False        # 16-bit serving: softmax weights enter the weighted sum with ~16 bits of mantissa
     gate_cap: float = 0.0             # mlstm: soft cap of the gate pre-activations (0 = none)
     state: int = 0                    # ssd: rows of a head's state
     groups: int = 1                   # ssd: groups of heads that share B / C
@@ -219,6 +220,7 @@ class ModelConfig:
     fp32_residual: bool = False       # the residual stream stays in fp32 whatever the compute dtype
     norm_bias: bool = True            # layer norms carry a bias
     logit_softcap: Optional[float] = None   # logits <- cap * tanh(logits / cap), after `logit_scale`
+    fp32_logits: bool = False         # 16-bit serving keeps the LM head's fp32 accumulator (no 16-bit rounding of logits)
     # looped span: layers loop_start .. loop_stop-1 run `loop_times` times in a row with the same weights; every pass
     # has caches / states of its own and starts by adding the embedding output (not the first pass) and a learned
     # vector of the pass to the stream

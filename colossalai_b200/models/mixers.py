@@ -104,7 +104,8 @@ class BiasSinkAttention(_MixerBase):
             lut = self._aux("lut", x.device, lambda: mops.bucket_lut(
                 mops.log_bucket_starts(sp.bias_buckets, sp.bias_max)))
         o = kv_cache.attend_ragged(self.layer_idx, q, k, v, self.scale, bias_table=table, bucket_starts=starts,
-                                   sink=sp.sink, v_other=v_other, lam=lam, lut=lut, mask_block=sp.mask_block)
+                                   sink=sp.sink, v_other=v_other, lam=lam, lut=lut, mask_block=sp.mask_block,
+                                   wide_weights=sp.wide_weights)
         if sp.out_gate:
             o = mops.sigmoid_gate_mul(o, gate)
         return self.o_proj(o)

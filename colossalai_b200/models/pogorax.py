@@ -40,7 +40,7 @@ def _attention_spec(m: dict, unit_norm: bool, gated: bool) -> MixerSpec:
     return MixerSpec(kind="attention", heads=m["heads"], kv_heads=m.get("kv_heads", m["heads"]), dim=m["dim"],
                      vdim=m.get("vdim", m["dim"]), scale=m["scale"], rot_dims=int(rot.get("dims", 0)),
                      rot_base=float(rot.get("base", 10000.0)), rot_interleaved=True, head_unit_norm=unit_norm,
-                     mask_block=int(mask.get("size", 0)), out_gate=gated)
+                     mask_block=int(mask.get("size", 0)), out_gate=gated, wide_weights=True)
 
 
 def pogorax_config(hf: dict, shapes: Optional[Dict[str, Tuple[int, ...]]] = None) -> ModelConfig:
@@ -74,7 +74,7 @@ def pogorax_config(hf: dict, shapes: Optional[Dict[str, Tuple[int, ...]]] = None
     return ModelConfig(model_type="pogorax", vocab_size=hf["vocab"], hidden_size=hf["width"],
                        intermediate_size=max(ffs) if ffs else hf["width"], layer_specs=specs,
                        norm_eps=hf["norm"]["eps"], norm_type="rms", hidden_act="gelu_tanh", glu=True, pos_type="none",
-                       embed_scale=hf.get("embedding", {}).get("scale", 1.0), fp32_residual=True,
+                       embed_scale=hf.get("embedding", {}).get("scale", 1.0), fp32_residual=True, fp32_logits=True,
                        tie_word_embeddings=False, max_position_embeddings=1 << 20)
 
 

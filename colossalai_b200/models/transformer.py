@@ -738,9 +738,10 @@ class TransformerLMHeadModel(nn.Module):
             w = F.normalize(self.lm_head.weight, dim=-1)
             logits = F.linear(h, w) if isinstance(self.lm_head, nn.Linear) else \
                 torch.func.functional_call(self.lm_head, {"weight": w}, (h,))
-        elif cfg.logit_softcap and h.is_cuda and h.dtype != torch.float32 and type(self.lm_head) is nn.Linear \
+        elif (cfg.logit_softcap or cfg.fp32_logits) and h.is_cuda and h.dtype != torch.float32 \
+                and type(self.lm_head) is nn.Linear \
                 and self.lm_head.bias is None and not torch.is_grad_enabled():
-            # soft-capped logits: the head's fp32 accumulator is kept (no 16-bit rounding in front of the tanh)
+            # the head's fp32 accumulator is kept (no 16-bit rounding in front of the soft cap's tanh / of the logits)
             logits = torch.mm(h, self.lm_head.weight.t(), out_dtype=torch.float32)
         else:
             logits = self.lm_head(h)

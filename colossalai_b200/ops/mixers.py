@@ -723,7 +723,7 @@ def paged_bias_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
                          meta: RaggedMeta, scale: float, bias_table: Optional[torch.Tensor] = None,
                          bucket_starts: Optional[torch.Tensor] = None, sink: bool = False,
                          lut: Optional[torch.Tensor] = None, tensor_cores: Optional[bool] = None,
-                         vdim: Optional[int] = None, mask_block: int = 0) -> torch.Tensor:
+                         vdim: Optional[int] = None, mask_block: int = 0, wide_weights: bool = False) -> torch.Tensor:
     """Causal attention of every step token over positions 0..pos of its sequence in the paged cache; with `mask_block`
     only over the positions of its own block, floor(pos / mask_block) * mask_block .. pos (blocks are counted from the
     start of the sequence, whatever the step's cut).
@@ -735,7 +735,9 @@ def paged_bias_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
 
     Two kernels: 16-bit inputs whose head widths are multiples of 8 up to 256 run on tensor cores (`lut` = `bucket_lut`
     of the same buckets; built here when absent); everything else - fp32 above all - takes the exact CUDA-core kernel.
-    `tensor_cores` forces the choice."""
+    `tensor_cores` forces the choice.  `wide_weights`: the tensor-core kernel feeds the softmax weights into the
+    weighted sum of the values as two 16-bit terms (value + rest of its rounding) instead of one, which keeps about 16
+    bits of every weight; the exact kernel holds them in fp32 anyway."""
     T = q.shape[0]
     _, bs, G, dim = k_cache.shape
     ldv = v_cache.shape[3]                     # elements between the value rows of consecutive (token, kv head) pairs
@@ -783,7 +785,8 @@ def paged_bias_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
                 loader.ptr(meta.cu_q), loader.ptr(meta.ctx_len), loader.ptr(meta.token_pos), loader.ptr(bias_table),
                 loader.ptr(lut), 0 if lut is None else lut.numel(), nb, loader.ptr(out), _i64(T), meta.nseq, meta.max_q,
                 heads, G, dim, vdim, ldv, bs, block_tables.shape[1], _f(scale), int(sink), chunk, splits,
-                loader.ptr(part_o), loader.ptr(part_ml), int(mask_block), code(q.dtype), loader.stream_ptr()),
+                loader.ptr(part_o), loader.ptr(part_ml), int(mask_block), int(wide_weights), code(q.dtype),
+                loader.stream_ptr()),
                 "paged_bias_attention_mma")
             loader.launch_counter.add("paged_bias_attention_mma")
             return out

@@ -2,10 +2,11 @@
 attention) beside a Llama of equal width, depth and head sizes, both with random weights through `LLMEngine`, plus the
 time of every mixer kernel alone against its roofline.  `--family palilix` runs the Palilix family (parallel layers with
 retention / latent attention, dense and routed feed-forwards, a looped span) beside Gopunex, the closest served family,
-at equal width and number of layer runs, and its kernels beside their like kernels.
+at equal width and number of layer runs, and its kernels beside their like kernels; `--family pogorax` does the same
+for the Pogorax family (pairs of attention and a recurrent mixer side by side, selective state spaces, pre-norm layers).
 
     python examples/inference/benchmark_hybrid.py [--sizes 2048x8,4096x4] [--batch 8] [--in_len 2048] [--out_len 64]
-                                                  [--family gopunex|palilix]
+                                                  [--family gopunex|palilix|pogorax]
 
 Also reachable as `python bench.py --workload hybrid-serve`.  One JSON line per (size, family) and one per kernel.
 Timing: CUDA events on the launching stream after warm-up; the kernel timings write a 256 MB buffer between runs (L2
@@ -68,6 +69,29 @@ def palilix_config(width: int, runs: int, vocab: int = 32000, kv_rank: int = 192
                        glu=False, pos_type="none", parallel_block=True, fp32_residual=True, embed_scale=1.0,
                        logit_scale=1.0, logit_softcap=30.0, loop_start=1, loop_stop=3, loop_times=2,
                        max_position_embeddings=1 << 20)
+
+
+def pogorax_config(width: int, layers: int, vocab: int = 32000) -> ModelConfig:
+    """Layers [rotary attention | linear recurrent unit, gated block-masked attention | matrix memory, state space, ...]:
+    attention heads of 128 (one key / value head per four query heads), rotary positions on half of every head, mask blocks
+    of 1024 positions; a recurrent unit as wide as the model with gate blocks of 128; matrix-memory heads of 64 x 128;
+    state-space heads of 64 channels with 128 state rows over twice the model width; gated feed-forwards of 8/3 x width
+    (none behind the state space)."""
+    H, d = width // 128, 128
+    G = max(H // 4, 1)
+    rot = MixerSpec(kind="attention", heads=H, kv_heads=G, dim=d, vdim=d, scale=d ** -0.5, rot_dims=64, rot_base=5e5,
+                    rot_interleaved=True, head_unit_norm=True, wide_weights=True)
+    lru = MixerSpec(kind="rglru", lru_width=width, blocks=H, conv=4)
+    gat = MixerSpec(kind="attention", heads=H, kv_heads=G, dim=d, vdim=d, scale=d ** -0.5, mask_block=1024, out_gate=True,
+                    wide_weights=True)
+    mem = MixerSpec(kind="mlstm", heads=H, dim=64, vdim=d, gate_cap=15.0)
+    ssd = MixerSpec(kind="ssd", heads=2 * width // 64, vdim=64, dim=128, state=128, groups=1, norm_groups=1, conv=4)
+    ff = width * 8 // 3 // 64 * 64
+    order = [(MixerSpec(kind="pair", parts=[rot, lru]), ff), (MixerSpec(kind="pair", parts=[gat, mem]), ff), (ssd, None)]
+    specs = [LayerSpec(mixer=order[i % 3][0], ff=order[i % 3][1]) for i in range(layers)]
+    return ModelConfig(model_type="pogorax", vocab_size=vocab, hidden_size=width, intermediate_size=ff, layer_specs=specs,
+                       norm_eps=1e-6, norm_type="rms", hidden_act="gelu_tanh", glu=True, pos_type="none", embed_scale=1.0,
+                       fp32_residual=True, fp32_logits=True, max_position_embeddings=1 << 20)
 
 
 def llama_config(width: int, layers: int, vocab: int = 32000) -> ModelConfig:
@@ -343,6 +367,126 @@ def kernels_palilix(width: int, batch: int, in_len: int, kv_rank: int = 192, rot
     return rows
 
 
+def kernels_pogorax(width: int, batch: int, in_len: int) -> list:
+    """Every kernel of the Pogorax layers alone at one layer's sizes beside its like kernel of the closest families."""
+    from colossalai_b200 import ops
+    from colossalai_b200.ops import mixers as M
+
+    hbm, tflops, src = peaks()
+    dev, dt = "cuda", torch.bfloat16
+    H, d, bs = width // 128, 128, 64
+    G = max(H // 4, 1)
+    flush = torch.zeros(64 << 20, dtype=torch.float32, device=dev)
+    rows = []
+
+    def rec(name, phase, ms, bytes_, flops, like=""):
+        ideal = max(bytes_ / hbm, flops / tflops) * 1e3
+        rows.append({"kernel": name, "phase": phase + ("(graph replay)" if phase == "decode" else ""), "width": width, "ms": ms, "roofline_ms": ideal,
+                     "frac_of_" + src + "_roofline": ideal / ms, "bound": "hbm" if bytes_ / hbm > flops / tflops else "tensor",
+                     "like": like})
+
+    for phase, q_len, ctx in (("prefill", in_len, 0), ("decode", 1, in_len)):
+        replay = phase == "decode"             # decode kernels are timed as graph replays (no host share)
+        T = batch * q_len
+        meta = M.RaggedMeta.build([q_len] * batch, [ctx] * batch, list(range(batch)), dev)
+        x = lambda c: torch.randn(T, c, device=dev, dtype=dt)
+        # stream sum + RMS norm, mean of two normed mixer outputs  |  like: Gopunex norm + residual
+        xs, y1, y2 = torch.randn(T, width, device=dev), x(width), x(width)
+        w = torch.ones(width, device=dev, dtype=dt)
+        ms = _time(lambda: M.stream_add_norm(xs, [y1], weight=w, eps=1e-6, kind="rms"), flush, graph=replay)
+        rec("stream_add_norm(1 addend, rms)", phase, ms, T * width * (4 + 4 + 2 + 2), 0, like="rmsnorm_residual")
+        ms = _time(lambda: M.norm_mean([y1, y2], [w, w], 1e-6), flush, graph=replay)
+        rec("norm_mean(2 parts)", phase, ms, T * width * (2 + 2 + 4), 0, like="rmsnorm_residual")
+        ms = _time(lambda: M.rms_norm_residual(xs, y1, w, 1e-5, 0.7, 1.0), flush, graph=replay)
+        rec("gopunex:rmsnorm_residual", phase, ms, T * width * (4 + 4 + 2 + 2), 0)
+        # matrix memory (heads of 64 x 128), state space (width / 32 heads of 128 x 64)  |  like: the decay scan
+        Hm, dm = H, 64
+        S = torch.zeros(batch, Hm, dm, d, device=dev)
+        n_, m_ = torch.zeros(batch, Hm, dm, device=dev), torch.zeros(batch, Hm, device=dev)
+        q, k, v, gates = x(Hm * dm) * 0.1, x(Hm * dm) * 0.1, x(Hm * d), x(2 * Hm)
+        gb = torch.zeros(2 * Hm, device=dev)
+        ms = _time(lambda: M.state_scan_mlstm(q, k, v, gates, gb, 15.0, S, n_, m_, meta, Hm, dm, d, dm ** -0.5), flush,
+                   graph=replay)
+        rec("state_scan_mlstm", phase, ms, T * (2 * Hm * dm * 2 + Hm * d * 2 + Hm * d * 4) + 2 * S.numel() * 4,
+            4.0 * T * Hm * dm * d, like="state_scan_decay")
+        Hs, N, dv = 2 * width // 64, 128, 64
+        Ss = torch.zeros(batch, Hs, N, dv, device=dev)
+        c_, b_, xs_, dtr = x(N), x(N), x(Hs * dv), x(Hs)
+        z3 = torch.zeros(Hs, device=dev)
+        ms = _time(lambda: M.state_scan_ssd(c_, b_, xs_, dtr, z3, z3, z3, Ss, meta, Hs, 1, N, dv), flush, graph=replay)
+        rec("state_scan_ssd", phase, ms, T * (2 * N * 2 + Hs * dv * 2 + Hs * dv * 4) + 2 * Ss.numel() * 4,
+            4.0 * T * Hs * N * dv, like="state_scan_decay")
+        Sg = torch.zeros(batch, H, d, d, device=dev)
+        qg, kg, vg = x(H * d) * 0.1, x(H * d) * 0.1, x(H * d)
+        dec = torch.full((H,), 0.97, device=dev)
+        ms = _time(lambda: M.state_scan_decay(qg, kg, vg, dec, Sg, meta, H, d, d), flush, graph=replay)
+        rec("gopunex:state_scan_decay", phase, ms, T * (3 * H * d * 2 + H * d * 4) + 2 * Sg.numel() * 4, 4.0 * T * H * d * d)
+        # linear recurrent unit: one thread per channel  |  like: the convolution (the other per-channel walk over time)
+        C = width
+        u, br = x(C), x(C)
+        gts = torch.randn(H, T, 2 * C // H, device=dev)
+        gbi, lam, Sl = torch.zeros(H, 2 * C // H, device=dev), torch.zeros(C, device=dev), torch.zeros(batch, C, device=dev)
+        ms = _time(lambda: M.lru_scan(u, gts, gbi, lam, br, Sl, meta), flush, graph=replay)
+        rec("lru_scan", phase, ms, T * C * (8 + 2 + 2 + 2), 0, like="short_conv_silu")
+        Cc = 2 * width + 2 * N
+        xc, wc, bc = x(Cc), torch.randn(Cc, 4, device=dev, dtype=dt), torch.randn(Cc, device=dev, dtype=dt)
+        st = torch.zeros(batch, 3, Cc, device=dev, dtype=dt)
+        ms = _time(lambda: M.short_conv_silu(xc, wc, st, meta, bias=bc), flush, graph=replay)
+        rec("short_conv_silu(bias)", phase, ms, 2 * T * Cc * 2, 0, like="short_conv_silu")
+        ms = _time(lambda: M.short_conv_silu(xc, wc, st, meta), flush, graph=replay)
+        rec("gopunex:short_conv_silu", phase, ms, 2 * T * Cc * 2, 0)
+        # gate-first group norm (state space), head norm (matrix memory)  |  like: the gated group norm
+        o, gate, wn = torch.randn(T, 2 * width, device=dev), x(2 * width), torch.ones(2 * width, device=dev, dtype=dt)
+        ms = _time(lambda: M.gated_group_rms_norm(o, wn, gate, 2 * width, 1e-6, dt, gate_act="silu", gate_first=True), flush,
+                   graph=replay)
+        rec("gated_group_rmsnorm(gate first, one group)", phase, ms, T * 2 * width * (4 + 2 + 2), 0, like="gated_group_rmsnorm")
+        wh = torch.ones(d, device=dev, dtype=dt)
+        ms = _time(lambda: M.gated_group_rms_norm(o, wh, gate, d, 1e-6, dt), flush, graph=replay)
+        rec("gopunex:gated_group_rmsnorm", phase, ms, T * 2 * width * (4 + 2 + 2), 0)
+        # rotary pairs + unit norm of q | k heads in place  |  like: Llama's in-place rotation
+        L = ctx + q_len
+        qkv = x((H + 2 * G) * d)
+        tab = M.rotary_table(L, 64, 5e5, dev)
+        ms = _time(lambda: M.rotary_unit_norm(qkv, H + G, d, 64, True, tab, meta.token_pos, 1e-6), flush, graph=replay)
+        rec("rotary_unit_norm", phase, ms, 2 * T * (H + G) * d * 2, 0, like="rope_qkv")
+        cos, sin = ops.build_rope_cache(L, d, 5e5, device=dev)
+        posl = meta.token_pos.long()
+        ms = _time(lambda: ops.rope_qkv(qkv, posl, cos, sin, H, G, d), flush, graph=replay)
+        rec("llama:rope_qkv", phase, ms, 2 * T * (H + G) * d * 2, 0)
+        og, gg = x(H * d), x(H * d)
+        ms = _time(lambda: M.sigmoid_gate_mul(og, gg), flush, graph=replay)
+        rec("sigmoid_gate_mul", phase, ms, 3 * T * H * d * 2, 0, like="glu_fwd(silu)")
+        gu = x(2 * H * d)
+        ms = _time(lambda: ops.glu(gu, "silu"), flush, graph=replay)
+        rec("llama:glu_fwd(silu)", phase, ms, 3 * T * H * d * 2, 0)
+        # attention over pages: causal and block-masked, both with two-term weights  |  like: bias + sink attention
+        per = (L + bs - 1) // bs
+        kc = torch.randn(batch * per, bs, G, d, device=dev, dtype=dt)
+        vc = torch.randn(batch * per, bs, G, d, device=dev, dtype=dt)
+        tables = torch.arange(batch * per, dtype=torch.int32, device=dev).view(batch, per)
+        qa = x(H * d)
+        kv_bytes = 2 * batch * L * G * d * 2
+        att_flops = 4.0 * batch * H * d * (q_len * ctx + q_len * (q_len + 1) / 2)
+        ms = _time(lambda: M.paged_bias_attention(qa, kc, vc, tables, meta, d ** -0.5, wide_weights=True), flush, graph=replay)
+        rec("paged_attention(causal, two-term weights)", phase, ms, kv_bytes + 2 * T * H * d * 2, 1.5 * att_flops,
+            like="paged_bias_attention")
+        mb = 1024
+        seen = sum(min(p_ % mb + 1, p_ + 1) for p_ in range(ctx, L)) * batch        # keys every query sees
+        ms = _time(lambda: M.paged_bias_attention(qa, kc, vc, tables, meta, d ** -0.5, mask_block=mb, wide_weights=True),
+                   flush, graph=replay)
+        rec("paged_attention(blocks of 1024, two-term weights)", phase, ms,
+            2 * batch * min(L, mb + q_len) * G * d * 2 + 2 * T * H * d * 2, 1.5 * 4.0 * H * d * seen,
+            like="paged_bias_attention")
+        rel = torch.randn(32, H, device=dev)
+        starts_host = M.log_bucket_starts(32, 512.0)
+        starts = torch.tensor(starts_host, dtype=torch.int32, device=dev)
+        lut = M.bucket_lut(starts_host).to(dev)
+        ms = _time(lambda: M.paged_bias_attention(qa, kc, vc, tables, meta, d ** -0.5, rel, starts, True, lut=lut), flush,
+                   graph=replay)
+        rec("gopunex:paged_bias_attention", phase, ms, kv_bytes + 2 * T * H * d * 2, att_flops)
+    return rows
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--sizes", default="2048x8,4096x4", help="width x layers, comma separated")
@@ -350,8 +494,9 @@ def main(argv=None):
     ap.add_argument("--in_len", type=int, default=2048)
     ap.add_argument("--out_len", type=int, default=32)
     ap.add_argument("--cuda_graph", action="store_true", help="also run both families with CUDA-graph decode steps")
-    ap.add_argument("--family", default="gopunex", choices=["gopunex", "palilix"],
-                    help="gopunex: the hybrid decoder beside Llama (default).  palilix: the Palilix family beside Gopunex")
+    ap.add_argument("--family", default="gopunex", choices=["gopunex", "palilix", "pogorax"],
+                    help="gopunex: the hybrid decoder beside Llama (default).  palilix / pogorax: that family beside "
+                         "Gopunex, the closest served family")
     ap.add_argument("--no-kernels", action="store_true")
     ap.add_argument("--no-serve", action="store_true")
     args = ap.parse_args(argv)
@@ -360,12 +505,14 @@ def main(argv=None):
         width, layers = (int(z) for z in size.split("x"))
         if not args.no_serve:
             for graph in ([False, True] if args.cuda_graph else [False]):
-                pair = (hybrid_config(width, layers), llama_config(width, layers)) if args.family == "gopunex" else \
-                    (palilix_config(width, layers), hybrid_config(width, layers))
+                pair = {"gopunex": lambda: (hybrid_config(width, layers), llama_config(width, layers)),
+                        "palilix": lambda: (palilix_config(width, layers), hybrid_config(width, layers)),
+                        "pogorax": lambda: (pogorax_config(width, layers), hybrid_config(width, layers))}[args.family]()
                 for cfg in pair:
                     print(json.dumps(serve(cfg, args.batch, args.in_len, args.out_len, graph)), flush=True)
         if not args.no_kernels:
-            for row in (kernels if args.family == "gopunex" else kernels_palilix)(width, args.batch, args.in_len):
+            kfn = {"gopunex": kernels, "palilix": kernels_palilix, "pogorax": kernels_pogorax}[args.family]
+            for row in kfn(width, args.batch, args.in_len):
                 print(json.dumps(row), flush=True)
 
 
