@@ -635,6 +635,55 @@ __global__ void __launch_bounds__(256) gated_group_rmsnorm_kernel(const float* _
   }
 }
 
+// wide groups (a state space's whole inner width is one group): one CTA per (token, group), four channels per thread and
+// step (16-byte reads of o, 8-byte ones of 16-bit operands; the launcher checks widths and alignment)
+template <typename T>
+__global__ void __launch_bounds__(256) gated_group_rmsnorm_wide_kernel(const float* __restrict__ o, const T* __restrict__ w,
+                                                                       int wn, const T* __restrict__ gate, int64_t ldg,
+                                                                       T* __restrict__ out, int C, int group, float eps,
+                                                                       int flags) {
+  struct alignas(sizeof(T) * 4) Pack { T v[4]; };
+  __shared__ float red[32];
+  const bool gate_silu = flags & 1;
+  const bool gate_first = (flags & 2) && gate != nullptr;
+  const int ngroups = C / group;
+  const int64_t t = blockIdx.x / ngroups;
+  const int c0 = (int)(blockIdx.x % ngroups) * group;
+  const float* row = o + t * C + c0;
+  const T* grow = gate != nullptr ? gate + t * ldg + c0 : nullptr;
+  float ss[1] = {0.f};
+  for (int i = threadIdx.x * 4; i < group; i += blockDim.x * 4) {
+    float4 v = *reinterpret_cast<const float4*>(row + i);
+    if (gate_first) {
+      const Pack g = *reinterpret_cast<const Pack*>(grow + i);
+      const float g0 = to_f32<T>(g.v[0]), g1 = to_f32<T>(g.v[1]), g2 = to_f32<T>(g.v[2]), g3 = to_f32<T>(g.v[3]);
+      v.x *= gate_silu ? silu_f(g0) : sigmoid_f(g0); v.y *= gate_silu ? silu_f(g1) : sigmoid_f(g1);
+      v.z *= gate_silu ? silu_f(g2) : sigmoid_f(g2); v.w *= gate_silu ? silu_f(g3) : sigmoid_f(g3);
+    }
+    ss[0] = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss[0]))));
+  }
+  block_sum<1>(ss, red);
+  const float r = 1.f / sqrtf(ss[0] / (float)group + eps);
+  for (int i = threadIdx.x * 4; i < group; i += blockDim.x * 4) {
+    const float4 v4 = *reinterpret_cast<const float4*>(row + i);
+    float v[4] = {v4.x, v4.y, v4.z, v4.w};
+    Pack g, res;
+    if (gate != nullptr) g = *reinterpret_cast<const Pack*>(grow + i);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      float y = v[e];
+      const float gv = gate != nullptr ? to_f32<T>(g.v[e]) : 0.f;
+      const float ga = gate_silu ? silu_f(gv) : sigmoid_f(gv);
+      if (gate_first) y *= ga;
+      y *= r;
+      if (w != nullptr) y *= to_f32<T>(w[(c0 + i + e) % wn]);
+      if (gate != nullptr && !gate_first) y *= ga;
+      res.v[e] = from_f32<T>(y);
+    }
+    *reinterpret_cast<Pack*>(out + t * C + c0 + i) = res;
+  }
+}
+
 // one CTA per token row.  x (fp32) += mult * y / rms(y) * (offset + w); h = cast(x).  VEC = 4: 16-byte accesses of the
 // stream, 8-byte ones of 16-bit operands (row width and strides multiples of 4, checked by the launcher).
 template <typename T, int VEC>
@@ -1653,6 +1702,56 @@ __global__ void __launch_bounds__(128) rotary_unit_norm_kernel(T* __restrict__ x
   }
 }
 
+// Interleaved pairs sit side by side, so a lane that holds four adjacent channels turns two whole pairs by itself: no
+// staging, 8-byte (16-bit types) or 16-byte (fp32) accesses.  One warp per (token, head); head widths up to 512 that
+// are multiples of 4, rot_dims a multiple of 4 too (the launcher checks, alignment included).
+template <typename T>
+__global__ void __launch_bounds__(128) rotary_pairs_unit_norm_kernel(T* __restrict__ x, int64_t ldx, int64_t tokens,
+                                                                     int heads, int dim, int rot_dims,
+                                                                     const float* __restrict__ table,
+                                                                     const int* __restrict__ token_pos, int unit,
+                                                                     float eps) {
+  struct alignas(sizeof(T) * 4) Pack { T v[4]; };
+  const int lane = threadIdx.x & 31;
+  const int64_t item = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= tokens * heads) return;
+  const int64_t t = item / heads;
+  T* row = x + t * ldx + (int64_t)(item % heads) * dim;
+  const int half = rot_dims >> 1;
+  const float* cs = rot_dims > 0 ? table + (int64_t)token_pos[t] * rot_dims : nullptr;
+  float y[4][4];
+  float ss = 0.f;
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const int c = (lane + 32 * e) * 4;
+    if (c < dim) {
+      const Pack a = *reinterpret_cast<const Pack*>(row + c);
+      float v0 = to_f32<T>(a.v[0]), v1 = to_f32<T>(a.v[1]), v2 = to_f32<T>(a.v[2]), v3 = to_f32<T>(a.v[3]);
+      if (c < rot_dims) {
+        const float2 cc = *reinterpret_cast<const float2*>(cs + (c >> 1));
+        const float2 sn = *reinterpret_cast<const float2*>(cs + half + (c >> 1));
+        const float r0 = v0 * cc.x - v1 * sn.x, r1 = v1 * cc.x + v0 * sn.x;
+        const float r2 = v2 * cc.y - v3 * sn.y, r3 = v3 * cc.y + v2 * sn.y;
+        v0 = r0; v1 = r1; v2 = r2; v3 = r3;
+      }
+      y[e][0] = v0; y[e][1] = v1; y[e][2] = v2; y[e][3] = v3;
+      ss = fmaf(v0, v0, fmaf(v1, v1, fmaf(v2, v2, fmaf(v3, v3, ss))));
+    }
+  }
+  float r = 1.f;
+  if (unit) r = 1.f / sqrtf(warp_sum(ss) / (float)dim + eps);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const int c = (lane + 32 * e) * 4;
+    if (c < dim) {
+      Pack o;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) o.v[i] = from_f32<T>(y[e][i] * r);
+      *reinterpret_cast<Pack*>(row + c) = o;
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------------------ mean of normed outputs
 // One CTA per token row: out = (1 / n) sum_j p_j / sqrt(mean(p_j^2) + eps) * w_j over up to four [T, W] tensors (each the
 // 16-bit type T or fp32, its weight of the same type), fp32 out.
@@ -1663,6 +1762,40 @@ struct NormMeanArgs {
   bool f32[4];
   int n;
 };
+
+// two parts whose rows fit the CTA's registers (W <= 256 x 4 x ITEMS): every input is read once
+template <typename T, int ITEMS, int VEC>
+__global__ void __launch_bounds__(256) norm_mean2_kernel(NormMeanArgs g, float* __restrict__ out, int W, float eps) {
+  __shared__ float red[2 * 32];
+  const int64_t t = blockIdx.x;
+  float v[2][ITEMS][VEC];
+  float ss[2] = {0.f, 0.f};
+#pragma unroll
+  for (int j = 0; j < 2; ++j)
+#pragma unroll
+    for (int it = 0; it < ITEMS; ++it) {
+      const int i = (it * 256 + threadIdx.x) * VEC;
+      if (i < W) {
+        load_vec<T, VEC>(g.p[j], g.f32[j], t * g.ld[j] + i, v[j][it]);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) ss[j] = fmaf(v[j][it][e], v[j][it][e], ss[j]);
+      }
+    }
+  block_sum<2>(ss, red);
+  const float r0 = 0.5f / sqrtf(ss[0] / (float)W + eps), r1 = 0.5f / sqrtf(ss[1] / (float)W + eps);
+#pragma unroll
+  for (int it = 0; it < ITEMS; ++it) {
+    const int i = (it * 256 + threadIdx.x) * VEC;
+    if (i < W) {
+      float w0[VEC], w1[VEC], acc[VEC];
+      load_vec<T, VEC>(g.w[0], g.f32[0], i, w0);
+      load_vec<T, VEC>(g.w[1], g.f32[1], i, w1);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) acc[e] = v[0][it][e] * r0 * w0[e] + v[1][it][e] * r1 * w1[e];
+      store_vec<T, VEC>(out, true, t * W + i, acc);
+    }
+  }
+}
 
 template <typename T, int VEC>
 __global__ void __launch_bounds__(256) norm_mean_kernel(NormMeanArgs g, float* __restrict__ out, int W, float eps) {
@@ -1793,8 +1926,15 @@ int cb_gated_group_rmsnorm(const float* o, const void* w, int wn, const void* ga
   if (group <= 0 || C % group != 0) return (int)cudaErrorInvalidValue;
   const int64_t units = tokens * (C / group);
   CB_DISPATCH_FLOAT(dtype, T, {
-    gated_group_rmsnorm_kernel<T><<<(unsigned)((units + 7) / 8), 256, 0, st>>>(o, (const T*)w, wn, (const T*)gate, ldg,
-                                                                              (T*)out, tokens, C, group, eps, gate_silu);
+    const size_t al = 4 * sizeof(T);
+    const bool wide = group >= 512 && group % 4 == 0 && ((uintptr_t)o & 15) == 0 && ((uintptr_t)out % al) == 0 &&
+                      (gate == nullptr || (ldg % 4 == 0 && ((uintptr_t)gate % al) == 0));
+    if (wide)
+      gated_group_rmsnorm_wide_kernel<T><<<(unsigned)units, 256, 0, st>>>(o, (const T*)w, wn, (const T*)gate, ldg, (T*)out,
+                                                                         C, group, eps, gate_silu);
+    else
+      gated_group_rmsnorm_kernel<T><<<(unsigned)((units + 7) / 8), 256, 0, st>>>(o, (const T*)w, wn, (const T*)gate, ldg,
+                                                                                (T*)out, tokens, C, group, eps, gate_silu);
   });
   return CB_LAUNCH_CHECK();
 }
@@ -2040,8 +2180,15 @@ int cb_rotary_unit_norm(void* x, int64_t ldx, int64_t tokens, int heads, int dim
     return (int)cudaErrorInvalidValue;
   const int64_t items = tokens * heads;
   CB_DISPATCH_FLOAT(dtype, T, {
-    rotary_unit_norm_kernel<T><<<(unsigned)((items + 3) / 4), 128, (size_t)4 * dim * sizeof(float), st>>>(
-        (T*)x, ldx, tokens, heads, dim, rot_dims, interleaved, table, token_pos, unit, eps);
+    const size_t al = 4 * sizeof(T);
+    const bool vec = (interleaved || rot_dims == 0) && dim % 4 == 0 && rot_dims % 4 == 0 && ldx % 4 == 0 &&
+                     ((uintptr_t)x % al) == 0 && ((uintptr_t)table & 7) == 0;
+    if (vec)
+      rotary_pairs_unit_norm_kernel<T><<<(unsigned)((items + 3) / 4), 128, 0, st>>>((T*)x, ldx, tokens, heads, dim, rot_dims,
+                                                                                   table, token_pos, unit, eps);
+    else
+      rotary_unit_norm_kernel<T><<<(unsigned)((items + 3) / 4), 128, (size_t)4 * dim * sizeof(float), st>>>(
+          (T*)x, ldx, tokens, heads, dim, rot_dims, interleaved, table, token_pos, unit, eps);
   });
   return CB_LAUNCH_CHECK();
 }
@@ -2072,7 +2219,18 @@ int cb_norm_mean(const void* p0, int64_t ld0, const void* w0, int dt0, const voi
   g.n = n;
   if (half_type == CB_F32) half_type = CB_BF16;      // no 16-bit operand: the type only names the unused branch
   CB_DISPATCH_HALF(half_type, T, {
-    if (vec) norm_mean_kernel<T, 4><<<(unsigned)tokens, 256, 0, st>>>(g, out, W, eps);
+    // 16-byte reads of two 16-bit parts where widths and addresses allow, else 8-byte ones
+    bool vec8 = vec && n == 2 && W % 8 == 0 && ((uintptr_t)out & 31) == 0;
+    for (int j = 0; j < 2 && vec8; ++j)
+      vec8 = dts[j] != CB_F32 && lds[j] % 8 == 0 && ((uintptr_t)ps[j] & 15) == 0 && ((uintptr_t)ws[j] & 15) == 0;
+    if (vec8 && W <= 2048) norm_mean2_kernel<T, 1, 8><<<(unsigned)tokens, 256, 0, st>>>(g, out, W, eps);
+    else if (vec8 && W <= 4096) norm_mean2_kernel<T, 2, 8><<<(unsigned)tokens, 256, 0, st>>>(g, out, W, eps);
+    else if (vec8 && W <= 8192) norm_mean2_kernel<T, 4, 8><<<(unsigned)tokens, 256, 0, st>>>(g, out, W, eps);
+    else if (vec && n == 2 && W <= 1024) norm_mean2_kernel<T, 1, 4><<<(unsigned)tokens, 256, 0, st>>>(g, out, W, eps);
+    else if (vec && n == 2 && W <= 2048) norm_mean2_kernel<T, 2, 4><<<(unsigned)tokens, 256, 0, st>>>(g, out, W, eps);
+    else if (vec && n == 2 && W <= 4096) norm_mean2_kernel<T, 4, 4><<<(unsigned)tokens, 256, 0, st>>>(g, out, W, eps);
+    else if (vec && n == 2 && W <= 8192) norm_mean2_kernel<T, 8, 4><<<(unsigned)tokens, 256, 0, st>>>(g, out, W, eps);
+    else if (vec) norm_mean_kernel<T, 4><<<(unsigned)tokens, 256, 0, st>>>(g, out, W, eps);
     else norm_mean_kernel<T, 1><<<(unsigned)tokens, 256, 0, st>>>(g, out, W, eps);
   });
   return CB_LAUNCH_CHECK();

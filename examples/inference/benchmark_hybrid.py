@@ -468,14 +468,15 @@ def kernels_pogorax(width: int, batch: int, in_len: int) -> list:
         kv_bytes = 2 * batch * L * G * d * 2
         att_flops = 4.0 * batch * H * d * (q_len * ctx + q_len * (q_len + 1) / 2)
         ms = _time(lambda: M.paged_bias_attention(qa, kc, vc, tables, meta, d ** -0.5, wide_weights=True), flush, graph=replay)
-        rec("paged_attention(causal, two-term weights)", phase, ms, kv_bytes + 2 * T * H * d * 2, 1.5 * att_flops,
+        # (rooflines count the algorithm's FLOPs: the second term of the weights is overhead, not work)
+        rec("paged_attention(causal, two-term weights)", phase, ms, kv_bytes + 2 * T * H * d * 2, att_flops,
             like="paged_bias_attention")
         mb = 1024
         seen = sum(min(p_ % mb + 1, p_ + 1) for p_ in range(ctx, L)) * batch        # keys every query sees
         ms = _time(lambda: M.paged_bias_attention(qa, kc, vc, tables, meta, d ** -0.5, mask_block=mb, wide_weights=True),
                    flush, graph=replay)
         rec("paged_attention(blocks of 1024, two-term weights)", phase, ms,
-            2 * batch * min(L, mb + q_len) * G * d * 2 + 2 * T * H * d * 2, 1.5 * 4.0 * H * d * seen,
+            2 * batch * min(L, mb + q_len) * G * d * 2 + 2 * T * H * d * 2, 4.0 * H * d * seen,
             like="paged_bias_attention")
         rel = torch.randn(32, H, device=dev)
         starts_host = M.log_bucket_starts(32, 512.0)

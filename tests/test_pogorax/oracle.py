@@ -85,8 +85,8 @@ def softmax_attention(h, W, p, mx, eps, pos, unit_norm, gated):
         for i in range(L):
             first = (pos[i] // size) * size if size else 0
             js = [j for j in range(L) if first <= pos[j] <= pos[i]]
-            s = torch.stack([q[i, n] @ k[j, g] for j in js]) * mx["scale"]
-            out[i, n] = torch.softmax(s, 0) @ torch.stack([v[j, g] for j in js])
+            s = (k[js, g] @ q[i, n]) * mx["scale"]
+            out[i, n] = torch.softmax(s, 0) @ v[js, g]
     o = out.reshape(L, H * dv)
     if gated:
         o = o * torch.sigmoid(h @ W[p + "g"].T)
