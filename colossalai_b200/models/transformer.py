@@ -410,6 +410,7 @@ class DecoderLayer(nn.Module):
         is left PENDING and added, in fp32, by the kernel that normalises the stream for the next sublayer (this
         layer's second norm, the next layer's first one, or the final norm): one pass over x per sublayer."""
         cfg = self.cfg
+        assert getattr(self.input_layernorm, "bias", None) is None, "the stream's fused norm carries a weight only"
         kw = dict(eps=cfg.norm_eps, kind=cfg.norm_type, offset=cfg.norm_weight_offset)
         h = ops.mixers.stream_add_norm(x, meta.pending or (), row=meta.pending_row, weight=self.input_layernorm.weight, **kw)
         meta.pending_row = None

@@ -23,7 +23,7 @@ MODELS = {
     # every mixer once, a layer without feed-forward in the middle
     "mixed": dict(layers=[O.rotary_pair_layer(), O.gated_pair_layer(), O.state_space_layer(), O.rotary_pair_layer(
         heads=6, kv_heads=2, dim=8, vdim=24, rot_dims=4, width=24, blocks=3, conv=3)]),
-    # state space first and last, with a feed-forward; sizes the task's habits would hide: one head, one group, one block,
+    # state space first and last, with a feed-forward; sizes that usual choices would hide: one head, one group, one block,
     # a convolution of two taps, a mask block of one page and a half, value heads wider than key heads
     "ones": dict(layers=[O.state_space_layer(heads=1, vdim=40, state=24, groups=1, norm_groups=1, conv=2, mlp="dense"),
                          O.gated_pair_layer(heads=1, kv_heads=1, dim=24, vdim=40, mask=12, m_heads=1, m_dim=40, m_vdim=8,
