@@ -138,9 +138,11 @@ def test_stream_after_every_layer(tmp_path, tier):
 
 
 @pytest.mark.parametrize("tier", TIERS)
-def test_bfloat16_serving_stays_within_rounding(tmp_path, tier):
+@pytest.mark.parametrize("name", list(MODELS))
+def test_bfloat16_serving_stays_within_rounding(tmp_path, tier, name):
+    """16-bit serving of every test model: also the widths that leave the kernels' vector paths."""
     _tier(tier)
-    path, cfg, W = _model(tmp_path, "mixed", seed=3)
+    path, cfg, W = _model(tmp_path, name, seed=3)
     toks = _tokens(40, cfg["vocab"], 2)
     want = O.forward(cfg, W, toks)
     eng = _engine(path, dtype=torch.bfloat16)
