@@ -1,7 +1,7 @@
 """Fixed-size recurrent state per live sequence, beside the paged K / V of attention layers.
 
 A recurrent mixer (linear attention, retention, delta rule, selective state space, gated matrix memory, gated linear
-recurrence) keeps, per sequence, fp32 memories ("S" and, for the gated matrix memory, the normaliser "n" and the running
+recurrence; also attention whose q / k pass a short convolution, which carries the convolution's window only) keeps, per sequence, fp32 memories ("S" and, for the gated matrix memory, the normaliser "n" and the running
 maximum "m") and - where it has short convolutions - the last few inputs of every convolved channel ("conv", in the
 compute dtype).  A layer whose mixer is a pair of mixers holds the pages of its paged part and the state of its recurrent
 part.  The pool holds `max_batch_size` slots per such
@@ -61,6 +61,8 @@ def layer_state_shapes(model_config, layer: int, slots: int) -> Optional[Dict[st
     sp = None if sp is None else sp.recurrent_part
     if sp is None:
         return None
+    if sp.kind == "attention":            # attention behind a convolution on q | k: only the convolution's window
+        return {"conv": (slots, max(sp.conv - 1, 0), (sp.heads + sp.kv_heads) * sp.dim)}
     if sp.kind == "rglru":
         return {"S": (slots, sp.lru_width), "conv": (slots, max(sp.conv - 1, 0), sp.lru_width)}
     if sp.kind == "ssd":
@@ -69,7 +71,7 @@ def layer_state_shapes(model_config, layer: int, slots: int) -> Optional[Dict[st
     out = {"S": (slots, sp.heads, sp.dim, sp.vdim)}
     if sp.kind == "mlstm":
         out["n"], out["m"] = (slots, sp.heads, sp.dim), (slots, sp.heads)
-    if sp.kind == "channel_delta":        # a one-tap convolution carries nothing: an empty tensor keeps the call uniform
+    if sp.kind in ("channel_delta", "delta"):        # a one-tap convolution carries nothing: an empty tensor keeps the call uniform
         out["conv"] = (slots, max(sp.conv - 1, 0), 2 * sp.kv_heads * sp.dim + sp.heads * sp.vdim)
     return out
 

@@ -100,31 +100,38 @@ class PagedKVRuntime:
     def layer_state(self, layer_idx: int) -> dict:
         return self.states[self.cache_index(layer_idx)]
 
-    def attend_latent(self, layer_idx: int, q: torch.Tensor, scale: float, kv_rank: int) -> torch.Tensor:
+    def attend_latent(self, layer_idx: int, q: torch.Tensor, scale: float, kv_rank: int, window: int = 0,
+                      sink: bool = False, sink_values: Optional[torch.Tensor] = None,
+                      wide_weights: bool = False) -> torch.Tensor:
         """Latent attention over the layer's pages (rows [latent | rotated key part], written by the caller through
-        `latent_cache`): q [T, H x (kv_rank + rot)] against the whole row, values = the row's first `kv_rank` columns.
+        `latent_cache`): q [T, H x (kv_rank + rot)] against the whole row, values = the row's first `kv_rank` columns;
+        optionally inside a sliding `window` and with a sink (`sink_values`: its score per head) in the denominator.
         Returns [T, H x kv_rank]."""
         from ...ops import mixers as mops
 
         kc = self.k_caches[self.cache_index(layer_idx)]
-        return mops.paged_bias_attention(q, kc, kc, self.block_tables, self.ragged, scale, vdim=kv_rank)
+        return mops.paged_bias_attention(q, kc, kc, self.block_tables, self.ragged, scale, vdim=kv_rank, window=window,
+                                         sink=sink, sink_values=sink_values, wide_weights=wide_weights)
 
     def latent_cache(self, layer_idx: int) -> torch.Tensor:
         return self.k_caches[self.cache_index(layer_idx)]
 
     def attend_ragged(self, layer_idx: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float,
                       bias_table=None, bucket_starts=None, sink: bool = False, v_other=None,
-                      lam: float = 0.0, lut=None, mask_block: int = 0, wide_weights: bool = False) -> torch.Tensor:
+                      lam: float = 0.0, lut=None, mask_block: int = 0, wide_weights: bool = False,
+                      sink_values: Optional[torch.Tensor] = None, slopes: Optional[torch.Tensor] = None,
+                      window: int = 0) -> torch.Tensor:
         """Write the step's K / V rows (values optionally blended with `v_other`) into the layer's pages, then attend
         every step token over positions 0..pos of its sequence (with `mask_block`: over the positions of its own block
-        of that many positions only).  q [T, H x dim], k [T, G x dim], v [T, G x vdim]."""
+        of that many positions only; with `window`: over the last `window` positions; `slopes`: a linear distance
+        penalty per head; `sink_values`: the sink's score per head).  q [T, H x dim], k [T, G x dim], v [T, G x vdim]."""
         from ...ops import mixers as mops
 
         kc, vc = self.k_caches[self.cache_index(layer_idx)], self.v_caches[self.cache_index(layer_idx)]
         mops.paged_kv_write_mix(k, v, kc, vc, self.block_tables, self.ragged, v_other=v_other, lam=lam)
         return mops.paged_bias_attention(q, kc, vc, self.block_tables, self.ragged, scale, bias_table=bias_table,
                                          bucket_starts=bucket_starts, sink=sink, lut=lut, mask_block=mask_block,
-                                         wide_weights=wide_weights)
+                                         wide_weights=wide_weights, sink_values=sink_values, slopes=slopes, window=window)
 
     @classmethod
     def scratch(cls, cfg, batch: int, seqlen: int, device, dtype, block_size: int = 16) -> "PagedKVRuntime":

@@ -35,7 +35,11 @@
 //   cb_paged_kv_write_mix   K / V rows (different widths allowed) into the paged cache, V optionally blended with another
 //                           layer's values first
 //   cb_paged_bias_attention causal attention of every step token over its sequence's paged cache with
-//                           score = scale * q.k + table[bucket(distance)][head] and an optional zero-score sink
+//                           score = scale * q.k + table[bucket(distance)][head] - slope[head] * distance, an optional
+//                           sink (score 0 or learned per head) in the denominator, a block mask or a sliding window
+//   cb_depth_mix            weighted sum over the history of the fp32 stream (+ compute-dtype copy)
+//   cb_poly_norm            a N(z) + b N(z^2) + c N(z^3) + e with N = division by the row's root mean square
+//   cb_head_rmsnorm         RMS norm per head with a weight over the head's channels (query heads | key heads)
 #include "common.cuh"
 
 namespace {
@@ -198,13 +202,13 @@ __global__ void __launch_bounds__(128) short_conv_state_kernel(const T* __restri
 
 // ------------------------------------------------------------------------------------------------ recurrent state scan
 enum ScanMode : int { SCAN_DECAY = 0, SCAN_DELTA = 1, SCAN_GATED = 2 };
-enum GateKind : int { GATE_STEP = 1, GATE_EXP = 2 };
+enum GateKind : int { GATE_STEP = 1, GATE_EXP = 2, GATE_HEAD = 3 };
 constexpr int SCAN_TOK_TILE = 8;
 
 struct ScanParams {
   const void *q, *k, *v;        // [T, ld*]: q/k hold qk_heads x dim, v holds heads x vdim
   int64_t ldq, ldk, ldv;
-  const void* araw;             // delta: pre-activation of the decay [T, lda] (heads x dim)
+  const void* araw;             // delta: pre-activation of the decay [T, lda] (heads x dim; heads with GATE_HEAD)
   int64_t lda;
   const void* braw;             // delta: pre-activation of the write strength [T, ldb] (heads)
   int64_t ldb;
@@ -299,10 +303,14 @@ __global__ void __launch_bounds__(128) scan_prepare_kernel(ScanParams p, ScanWor
   if (MODE == SCAN_DELTA) {
     for (int h = warp; h < p.heads; h += nwarps) {
       const float A = expf(p.a_log[h]);
+      // GATE_HEAD: one decay per head (araw [T, heads], dt_bias [heads]) fills the head's row of channel decays
+      const float gh = p.gate_kind == GATE_HEAD
+                           ? expf(-A * softplus_f(to_f32<T>(((const T*)p.araw)[t * p.lda + h]) + p.dt_bias[h])) : 1.f;
       for (int i = lane; i < DK; i += 32) {
         float g = 1.f;
         if (i < dim)
-          g = expf(-A * softplus_f(to_f32<T>(((const T*)p.araw)[t * p.lda + h * dim + i]) + p.dt_bias[h * dim + i]));
+          g = p.gate_kind == GATE_HEAD ? gh
+              : expf(-A * softplus_f(to_f32<T>(((const T*)p.araw)[t * p.lda + h * dim + i]) + p.dt_bias[h * dim + i]));
         w.g[(t * p.heads + h) * DK + i] = g;
       }
     }
@@ -684,51 +692,126 @@ __global__ void __launch_bounds__(256) gated_group_rmsnorm_wide_kernel(const flo
   }
 }
 
-// one CTA per token row.  x (fp32) += mult * y / rms(y) * (offset + w); h = cast(x).  VEC = 4: 16-byte accesses of the
-// stream, 8-byte ones of 16-bit operands (row width and strides multiples of 4, checked by the launcher).
-template <typename T, int VEC>
-__global__ void __launch_bounds__(256) rmsnorm_residual_kernel(float* __restrict__ x, const T* __restrict__ y, int64_t ldy,
+// one CTA per (token row, norm group).  x (fp32) += mult * y / rms_group(y) * (offset + w); h = cast(x): the row is cut into
+// `groups` equal consecutive parts and every part is divided by its own root mean square.  y is the 16-bit type T or
+// (TY = float) an fp32 sum.  VEC = 4: 16-byte accesses of the stream, 8-byte ones of 16-bit operands (group width and
+// strides multiples of 4, checked by the launcher).
+template <typename T, typename TY, int VEC>
+__global__ void __launch_bounds__(256) rmsnorm_residual_kernel(float* __restrict__ x, const TY* __restrict__ y, int64_t ldy,
                                                                const T* __restrict__ w, T* __restrict__ h, int W,
-                                                               float eps, float mult, float offset) {
+                                                               int groups, float eps, float mult, float offset) {
   struct alignas(sizeof(T) * VEC) Pack { T v[VEC]; };
+  struct alignas(sizeof(TY) * VEC) PackY { TY v[VEC]; };
   struct alignas(sizeof(float) * VEC) PackF { float v[VEC]; };
   __shared__ float red[64];
-  const int64_t t = blockIdx.x;
-  const T* yr = y + t * ldy;
+  const int64_t t = blockIdx.x / groups;
+  const int Wg = W / groups, c0 = (int)(blockIdx.x % groups) * Wg;
+  const TY* yr = y + t * ldy + c0;
   float ss[1] = {0.f};
-  for (int i = threadIdx.x * VEC; i < W; i += blockDim.x * VEC) {
-    const Pack a = *reinterpret_cast<const Pack*>(yr + i);
+  for (int i = threadIdx.x * VEC; i < Wg; i += blockDim.x * VEC) {
+    const PackY a = *reinterpret_cast<const PackY*>(yr + i);
 #pragma unroll
-    for (int e = 0; e < VEC; ++e) ss[0] = fmaf(to_f32<T>(a.v[e]), to_f32<T>(a.v[e]), ss[0]);
+    for (int e = 0; e < VEC; ++e) ss[0] = fmaf(to_f32<TY>(a.v[e]), to_f32<TY>(a.v[e]), ss[0]);
   }
   block_sum<1>(ss, red);
-  const float r = 1.f / sqrtf(ss[0] / (float)W + eps);
-  for (int i = threadIdx.x * VEC; i < W; i += blockDim.x * VEC) {
-    const Pack a = *reinterpret_cast<const Pack*>(yr + i);
-    const Pack ww = *reinterpret_cast<const Pack*>(w + i);
-    PackF xv = *reinterpret_cast<const PackF*>(x + t * W + i);
+  const float r = 1.f / sqrtf(ss[0] / (float)Wg + eps);
+  for (int i = threadIdx.x * VEC; i < Wg; i += blockDim.x * VEC) {
+    const PackY a = *reinterpret_cast<const PackY*>(yr + i);
+    const Pack ww = *reinterpret_cast<const Pack*>(w + c0 + i);
+    PackF xv = *reinterpret_cast<const PackF*>(x + t * W + c0 + i);
     Pack hv;
 #pragma unroll
     for (int e = 0; e < VEC; ++e) {
-      xv.v[e] += mult * (to_f32<T>(a.v[e]) * r * (offset + to_f32<T>(ww.v[e])));
+      xv.v[e] += mult * (to_f32<TY>(a.v[e]) * r * (offset + to_f32<T>(ww.v[e])));
       hv.v[e] = from_f32<T>(xv.v[e]);
     }
-    *reinterpret_cast<PackF*>(x + t * W + i) = xv;
-    if (h != nullptr) *reinterpret_cast<Pack*>(h + t * W + i) = hv;
+    *reinterpret_cast<PackF*>(x + t * W + c0 + i) = xv;
+    if (h != nullptr) *reinterpret_cast<Pack*>(h + t * W + c0 + i) = hv;
   }
 }
 
 template <typename T>
-__global__ void __launch_bounds__(256) rmsnorm_f32in_kernel(const float* __restrict__ x, const T* __restrict__ w,
-                                                            T* __restrict__ out, int W, float eps, float offset) {
+__global__ void __launch_bounds__(256) rmsnorm_f32in_kernel(const float* __restrict__ x, int64_t ldx,
+                                                            const T* __restrict__ w, T* __restrict__ out, int W,
+                                                            int groups, float eps, float offset) {
   __shared__ float red[64];
-  const int64_t t = blockIdx.x;
+  const int64_t t = blockIdx.x / groups;
+  const int Wg = W / groups, c0 = (int)(blockIdx.x % groups) * Wg;
+  const float* xr = x + t * ldx + c0;
   float ss[1] = {0.f};
-  for (int i = threadIdx.x; i < W; i += blockDim.x) ss[0] = fmaf(x[t * W + i], x[t * W + i], ss[0]);
+  for (int i = threadIdx.x; i < Wg; i += blockDim.x) ss[0] = fmaf(xr[i], xr[i], ss[0]);
   block_sum<1>(ss, red);
-  const float r = 1.f / sqrtf(ss[0] / (float)W + eps);
-  for (int i = threadIdx.x; i < W; i += blockDim.x)
-    out[t * W + i] = from_f32<T>(x[t * W + i] * r * (offset + to_f32<T>(w[i])));
+  const float r = 1.f / sqrtf(ss[0] / (float)Wg + eps);
+  for (int i = threadIdx.x; i < Wg; i += blockDim.x)
+    out[t * W + c0 + i] = from_f32<T>(xr[i] * r * (offset + to_f32<T>(w[c0 + i])));
+}
+
+// Weighted sum over the history of an fp32 residual stream: hist [n, T x W] (slices `stride` elements apart),
+// out = sum_j coef[j] hist[j] in ascending j (coef: n fp32 numbers on the device), written as fp32 and (optionally) in
+// the compute dtype for the next layer's GEMMs.  Four elements per thread, all n loads of a thread independent.
+template <typename T>
+__global__ void __launch_bounds__(256) depth_mix_kernel(const float* __restrict__ hist, int64_t stride, int n,
+                                                        const float* __restrict__ coef, float* __restrict__ out,
+                                                        T* __restrict__ h, int64_t total4) {
+  struct alignas(sizeof(T) * 4) Pack { T v[4]; };
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total4; i += (int64_t)gridDim.x * blockDim.x) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int j = 0; j < n; ++j) {
+      const float a = __ldg(coef + j);
+      const float4 v = *reinterpret_cast<const float4*>(hist + j * stride + i * 4);
+      acc.x = fmaf(a, v.x, acc.x); acc.y = fmaf(a, v.y, acc.y); acc.z = fmaf(a, v.z, acc.z); acc.w = fmaf(a, v.w, acc.w);
+    }
+    *reinterpret_cast<float4*>(out + i * 4) = acc;
+    if (h != nullptr) {
+      Pack p;
+      p.v[0] = from_f32<T>(acc.x); p.v[1] = from_f32<T>(acc.y); p.v[2] = from_f32<T>(acc.z); p.v[3] = from_f32<T>(acc.w);
+      *reinterpret_cast<Pack*>(h + i * 4) = p;
+    }
+  }
+}
+
+// Polynomial activation with normalised powers, one CTA per token row: out = a N(z) + b N(z^2) + c N(z^3) + e with powers
+// taken element by element and N(u) = u / sqrt(mean(u^2) + eps) over the row; the three sums of squares (z^2, z^4, z^6)
+// come from one pass, everything in fp32.  coef = (a, b, c, e) on the device.
+template <typename T>
+__global__ void __launch_bounds__(256) poly_norm_kernel(const T* __restrict__ z, int64_t ldz, T* __restrict__ out, int F,
+                                                        const float* __restrict__ coef, float eps) {
+  __shared__ float red[3 * 32];
+  const int64_t t = blockIdx.x;
+  const T* zr = z + t * ldz;
+  float ss[3] = {0.f, 0.f, 0.f};
+  for (int i = threadIdx.x; i < F; i += blockDim.x) {
+    const float v = to_f32<T>(zr[i]), v2 = v * v;
+    ss[0] += v2;
+    ss[1] = fmaf(v2, v2, ss[1]);
+    ss[2] = fmaf(v2 * v, v2 * v, ss[2]);
+  }
+  block_sum<3>(ss, red);
+  const float r1 = coef[0] / sqrtf(ss[0] / (float)F + eps), r2 = coef[1] / sqrtf(ss[1] / (float)F + eps),
+              r3 = coef[2] / sqrtf(ss[2] / (float)F + eps), e0 = coef[3];
+  for (int i = threadIdx.x; i < F; i += blockDim.x) {
+    const float v = to_f32<T>(zr[i]), v2 = v * v;
+    out[t * F + i] = from_f32<T>(fmaf(r1, v, fmaf(r2, v2, fmaf(r3, v2 * v, e0))));
+  }
+}
+
+// RMS norm of every head of a [T, heads x dim] projection with one weight over the head's channels, shared by the heads:
+// the first `heads_a` heads take `wa`, the others `wb` (query heads, then key heads).  One warp per (token, head), fp32.
+template <typename T>
+__global__ void __launch_bounds__(128) head_rmsnorm_kernel(const T* __restrict__ x, int64_t ldx, T* __restrict__ out,
+                                                           int64_t ldo, int64_t tokens, int heads, int heads_a, int dim,
+                                                           const T* __restrict__ wa, const T* __restrict__ wb, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int64_t unit = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (unit >= tokens * heads) return;
+  const int64_t t = unit / heads;
+  const int hd = (int)(unit % heads);
+  const T* row = x + t * ldx + hd * dim;
+  const T* w = hd < heads_a ? wa : wb;
+  float ss = 0.f;
+  for (int i = lane; i < dim; i += 32) { const float v = to_f32<T>(row[i]); ss = fmaf(v, v, ss); }
+  const float r = 1.f / sqrtf(warp_sum(ss) / (float)dim + eps);
+  for (int i = lane; i < dim; i += 32) out[t * ldo + hd * dim + i] = from_f32<T>(to_f32<T>(row[i]) * r * to_f32<T>(w[i]));
 }
 
 // ------------------------------------------------------------------------------------------------ stream sums + norm
@@ -1046,7 +1129,9 @@ __global__ void __launch_bounds__(128) paged_kv_write_mix_kernel(const T* __rest
 // ------------------------------------------------------------------------------------------------ paged attention
 // One warp per (step token, query head).  Keys 0..pos of the token's sequence are walked in tiles of 32 in a fixed order
 // (lane = key for the scores, lane = value channel for the weighted sum), online softmax in fp32.  With `sink` the running
-// maximum starts at 0 and the denominator at 1: a key of score 0 without a value.
+// maximum starts at the sink's score (`sink_vals[head]`, 0 without the table) and the denominator at 1: a key of that
+// score without a value, not scaled.  `slopes[head]` takes slope * (pos - key) off every score; `window` > 0 keeps the
+// keys pos - window + 1 .. pos only.
 constexpr int ATT_MAX_VREG = 16;  // value width up to 512
 
 template <typename T>
@@ -1055,7 +1140,7 @@ __global__ void __launch_bounds__(128) paged_bias_attention_kernel(
     const int* __restrict__ block_tables, const int* __restrict__ token_seq, const int* __restrict__ token_pos,
     const float* __restrict__ bias_table, const int* __restrict__ bucket_start, int nbuckets, T* __restrict__ out,
     int64_t tokens, int heads, int kv_heads, int dim, int vdim, int ldv, int block_size, int max_blocks, float scale,
-    int sink, int mask_block) {
+    int sink, int mask_block, const float* __restrict__ sink_vals, const float* __restrict__ slopes, int window) {
   extern __shared__ float smem[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   float* qs = smem + warp * dim;
@@ -1072,12 +1157,15 @@ __global__ void __launch_bounds__(128) paged_bias_attention_kernel(
   const int seq = token_seq[t], pos = token_pos[t];
   const int* bt = block_tables + (int64_t)seq * max_blocks;
   const int half = nbuckets >> 1;
-  float m = sink ? 0.f : -INFINITY, l = sink ? 1.f : 0.f;
+  float m = sink ? (sink_vals != nullptr ? sink_vals[h] : 0.f) : -INFINITY, l = sink ? 1.f : 0.f;
+  const float slope = slopes != nullptr ? slopes[h] : 0.f;
   float acc[ATT_MAX_VREG];
 #pragma unroll
   for (int r = 0; r < ATT_MAX_VREG; ++r) acc[r] = 0.f;
-  // with a block mask the keys start at the first position of the query's own block
-  for (int j0 = mask_block > 0 ? pos / mask_block * mask_block : 0; j0 <= pos; j0 += 32) {
+  // with a block mask the keys start at the first position of the query's own block, with a window at its first key
+  int jfirst = mask_block > 0 ? pos / mask_block * mask_block : 0;
+  if (window > 0) jfirst = max(jfirst, pos - window + 1);
+  for (int j0 = jfirst; j0 <= pos; j0 += 32) {
     const int jk = j0 + lane;
     float sc = -INFINITY;
     int64_t myrow = 0;
@@ -1101,6 +1189,7 @@ __global__ void __launch_bounds__(128) paged_bias_attention_kernel(
         }
         sc += bias_table[b * heads + h];
       }
+      sc -= slope * (float)(pos - jk);
     }
     const float mn = fmaxf(m, warp_max(sc));
     const float alpha = expf(m - mn);           // m = -inf only before the first tile without a sink: exp(-inf) = 0
@@ -1199,7 +1288,8 @@ __global__ void __launch_bounds__(128, D > 128 ? 1 : (MT == 2 ? 2 : 3)) paged_bi
     const int* __restrict__ block_tables, const int* __restrict__ cu_q, const int* __restrict__ ctx_len,
     const float* __restrict__ bias_table, const uint8_t* __restrict__ lut, int lut_n, int nbuckets, T* __restrict__ out,
     int heads, int kv_heads, int dim, int vdim, int ldv, int block_size, int max_blocks, float scale, int sink, int chunk,
-    int max_splits, float* __restrict__ part_o, float* __restrict__ part_ml, int mask_block, int wide_weights) {
+    int max_splits, float* __restrict__ part_o, float* __restrict__ part_ml, int mask_block, int wide_weights,
+    const float* __restrict__ sink_vals, const float* __restrict__ slopes, int window) {
   constexpr int BM = 64 * MT;
   constexpr int LDS = D + 8;                    // padded row: 16-byte aligned, conflict-free fragment reads
   constexpr int TILE = MMA_BN * LDS;
@@ -1226,7 +1316,14 @@ __global__ void __launch_bounds__(128, D > 128 ? 1 : (MT == 2 ? 2 : 3)) paged_bi
   // block mask: a row at position p sees keys p / mask_block * mask_block .. p; the tile's keys start at its first row's
   // block (key chunks that end below it are never read: the merge starts at the row's own first chunk)
   // (rounded down to a key tile, so that tiles keep their place inside a key chunk and never reach into the next one)
-  const int blk_lo = mask_block > 0 ? (ctx + row0 / R) / mask_block * mask_block / MMA_BN * MMA_BN : 0;
+  // A window of `window` positions moves a row's first key to pos - window + 1 in the same way (both grow with pos).
+  auto first_key = [&](int p) {
+    int f = mask_block > 0 ? p / mask_block * mask_block : 0;
+    if (window > 0) f = max(f, p - window + 1);
+    return f;
+  };
+  const bool masked_lo = mask_block > 0 || window > 0;
+  const int blk_lo = masked_lo ? first_key(ctx + row0 / R) / MMA_BN * MMA_BN : 0;
   const int key_lo = max(chunk > 0 ? split * chunk : 0, blk_lo);
   const int pos_max = chunk > 0 ? min(ctx + last_row / R, split * chunk + chunk - 1) : ctx + last_row / R;
   if (key_lo > pos_max) return;                 // this chunk lies beyond (or below) every row of the tile
@@ -1269,7 +1366,7 @@ __global__ void __launch_bounds__(128, D > 128 ? 1 : (MT == 2 ? 2 : 3)) paged_bi
     valid[e] = rr[e] < nrows;
     hr[e] = valid[e] ? rr[e] % R : 0;
     pos[e] = valid[e] ? ctx + rr[e] / R : -1;
-    lo[e] = (mask_block > 0 && valid[e]) ? pos[e] / mask_block * mask_block : 0;      // first key the row sees
+    lo[e] = (masked_lo && valid[e]) ? first_key(pos[e]) : 0;      // first key the row sees
   }
   float o[MT][D / 8][4];
 #pragma unroll
@@ -1278,10 +1375,13 @@ __global__ void __launch_bounds__(128, D > 128 ? 1 : (MT == 2 ? 2 : 3)) paged_bi
     for (int nv = 0; nv < D / 8; ++nv)
 #pragma unroll
       for (int e = 0; e < 4; ++e) o[mt][nv][e] = 0.f;
-  float m[NR], l[NR];
+  float m[NR], l[NR], sk[NR], sl[NR], slb[NR];
 #pragma unroll
   for (int e = 0; e < NR; ++e) {
-    m[e] = (sink && chunk == 0) ? 0.f : -INFINITY;          // log2 domain; with chunks the sink joins in the merge
+    sk[e] = (sink_vals != nullptr && valid[e]) ? sink_vals[g * R + hr[e]] * LOG2E : 0.f;      // the sink's score
+    sl[e] = (slopes != nullptr && valid[e]) ? slopes[g * R + hr[e]] * LOG2E : 0.f;            // score -= sl * (pos - key)
+    slb[e] = -sl[e] * (float)pos[e];
+    m[e] = (sink && chunk == 0) ? sk[e] : -INFINITY;        // log2 domain; with chunks the sink joins in the merge
     l[e] = 0.f;                                 // per-thread partial; the sink's share is added once at the end
   }
   const float sc2 = scale * LOG2E;
@@ -1291,7 +1391,7 @@ __global__ void __launch_bounds__(128, D > 128 ? 1 : (MT == 2 ? 2 : 3)) paged_bi
   const bool wlive = wrow0 < nrows;
   const int wlo = ctx + min(nrows - 1, wrow0) / R;
   const int whi = wlive ? ctx + min(nrows - 1, wrow0 + 16 * MT - 1) / R : -1;
-  const int wblk = (mask_block > 0 && wlive) ? whi / mask_block * mask_block : 0;     // latest block start among its rows
+  const int wblk = (masked_lo && wlive) ? first_key(whi) : 0;     // latest first key among its rows
   const uint32_t q_addr = (uint32_t)__cvta_generic_to_shared(Qs + ((KS ? 0 : warp * 16 * MT) + (lane & 15)) * LDS +
                                                              (lane >> 4) * 8);
 
@@ -1351,7 +1451,8 @@ __global__ void __launch_bounds__(128, D > 128 ? 1 : (MT == 2 ? 2 : 3)) paged_bi
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               const int r = mt * 2 + (e >> 1);
-              const float sv = fmaf(sacc[mt][nt][e], sc2, fb[r]);
+              float sv = fmaf(sacc[mt][nt][e], sc2, fb[r]);
+              if (slopes != nullptr) sv += fmaf(sl[r], (float)(j0 + koff + nt * 8 + tig * 2 + (e & 1)), slb[r]);
               sacc[mt][nt][e] = sv;
               mx[r] = fmaxf(mx[r], sv);
             }
@@ -1370,6 +1471,7 @@ __global__ void __launch_bounds__(128, D > 128 ? 1 : (MT == 2 ? 2 : 3)) paged_bi
                   const int n = pos[r] - j;
                   sv += n < lut_n ? tab[(int)__ldg(lut + n) * R + hr[r]] : fb[r];
                 }
+                if (slopes != nullptr) sv += fmaf(sl[r], (float)j, slb[r]);
               }
               sacc[mt][nt][e] = sv;
               mx[r] = fmaxf(mx[r], sv);
@@ -1483,7 +1585,7 @@ __global__ void __launch_bounds__(128, D > 128 ? 1 : (MT == 2 ? 2 : 3)) paged_bi
           part_ml[(unit * max_splits + split) * 2 + 1] = lsum;
         }
       } else {
-        if (sink) lsum += ex2f(0.f - mu);
+        if (sink) lsum += ex2f((sink_vals != nullptr ? sink_vals[g * R + row % R] * LOG2E : 0.f) - mu);
         out[unit * vdim + c] = from_f32<T>(lsum > 0.f ? osum / lsum : 0.f);
       }
     }
@@ -1509,7 +1611,7 @@ __global__ void __launch_bounds__(128, D > 128 ? 1 : (MT == 2 ? 2 : 3)) paged_bi
       }
       continue;
     }
-    if (sink) l[r] += ex2f(0.f - (m[r] == -INFINITY ? 0.f : m[r]));
+    if (sink) l[r] += ex2f(sk[r] - (m[r] == -INFINITY ? 0.f : m[r]));
     const float inv = l[r] > 0.f ? 1.f / l[r] : 0.f;
     T* orow = out + unit * vdim;
 #pragma unroll
@@ -1529,7 +1631,8 @@ __global__ void __launch_bounds__(128) attention_merge_kernel(const float* __res
                                                               const float* __restrict__ part_ml,
                                                               const int* __restrict__ token_pos, T* __restrict__ out,
                                                               int64_t tokens, int heads, int vdim, int chunk,
-                                                              int max_splits, int sink, int mask_block) {
+                                                              int max_splits, int sink, int mask_block,
+                                                              const float* __restrict__ sink_vals, int window) {
   const int lane = threadIdx.x & 31;
   const int cblocks = (vdim + 31) >> 5;
   const int64_t item = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -1538,15 +1641,18 @@ __global__ void __launch_bounds__(128) attention_merge_kernel(const float* __res
   const int c = (int)(item % cblocks) * 32 + lane;
   const int tpos = token_pos[unit / heads];
   const int nsp = tpos / chunk + 1;
-  const int sp0 = mask_block > 0 ? (tpos / mask_block * mask_block) / chunk : 0;      // first chunk with a visible key
+  int kfirst = mask_block > 0 ? tpos / mask_block * mask_block : 0;
+  if (window > 0) kfirst = max(kfirst, tpos - window + 1);
+  const int sp0 = kfirst / chunk;                                                     // first chunk with a visible key
   const float* ml = part_ml + unit * max_splits * 2;
-  float mm = sink ? 0.f : -INFINITY;
+  const float sk = sink_vals != nullptr ? sink_vals[unit % heads] * 1.4426950408889634f : 0.f;
+  float mm = sink ? sk : -INFINITY;
   for (int sp = sp0 + lane; sp < nsp; sp += 32) mm = fmaxf(mm, ml[sp * 2]);
   mm = warp_max(mm);
   const float mu = mm == -INFINITY ? 0.f : mm;
   float l = 0.f;
   for (int sp = sp0 + lane; sp < nsp; sp += 32) l = fmaf(ml[sp * 2 + 1], ex2f(ml[sp * 2] - mu), l);
-  l = warp_sum(l) + (sink ? ex2f(0.f - mu) : 0.f);
+  l = warp_sum(l) + (sink ? ex2f(sk - mu) : 0.f);
   float acc = 0.f;
   const float* po = part_o + unit * max_splits * vdim;
   for (int s0 = sp0; s0 < nsp; s0 += 32) {
@@ -1568,7 +1674,7 @@ int launch_attention_mma(const void* q, int64_t ldq, const void* k_cache, const 
                          const uint8_t* lut, int lut_n, int nbuckets, void* out, int64_t tokens, int nseq, int max_q,
                          int heads, int kv_heads, int dim, int vdim, int ldv, int block_size, int max_blocks, float scale,
                          int sink, int chunk, int max_splits, float* part_o, float* part_ml, int mask_block,
-                         int wide_weights, cudaStream_t st) {
+                         int wide_weights, const float* sink_vals, const float* slopes, int window, cudaStream_t st) {
   const int R = heads / kv_heads;
   constexpr int BM = 64 * MT;
   const bool kv_same = v_cache == k_cache && ldv == dim;
@@ -1585,11 +1691,13 @@ int launch_attention_mma(const void* q, int64_t ldq, const void* k_cache, const 
   dim3 grid(rowtiles * (chunk > 0 ? max_splits : 1), kv_heads, nseq);
   kern<<<grid, 128, smem, st>>>((const T*)q, ldq, (const T*)k_cache, (const T*)v_cache, block_tables, cu_q, ctx_len,
                                 bias_table, lut, lut_n, nbuckets, (T*)out, heads, kv_heads, dim, vdim, ldv, block_size,
-                                max_blocks, scale, sink, chunk, max_splits, part_o, part_ml, mask_block, wide_weights);
+                                max_blocks, scale, sink, chunk, max_splits, part_o, part_ml, mask_block, wide_weights,
+                                sink_vals, slopes, window);
   if (chunk > 0) {
     const int64_t units = tokens * heads * ((vdim + 31) / 32);
     attention_merge_kernel<T><<<(unsigned)((units + 3) / 4), 128, 0, st>>>(part_o, part_ml, token_pos, (T*)out, tokens,
-                                                                          heads, vdim, chunk, max_splits, sink, mask_block);
+                                                                          heads, vdim, chunk, max_splits, sink, mask_block,
+                                                                          sink_vals, window);
   }
   return CB_LAUNCH_CHECK();
 }
@@ -1939,27 +2047,76 @@ int cb_gated_group_rmsnorm(const float* o, const void* w, int wn, const void* ga
   return CB_LAUNCH_CHECK();
 }
 
-int cb_rmsnorm_residual(float* x, const void* y, int64_t ldy, const void* w, void* h, int64_t tokens, int W, float eps,
-                        float mult, float offset, int dtype, cudaStream_t st) {
+int cb_rmsnorm_residual(float* x, const void* y, int64_t ldy, int y_f32, const void* w, void* h, int64_t tokens, int W,
+                        int groups, float eps, float mult, float offset, int dtype, cudaStream_t st) {
   if (tokens == 0) return 0;
+  if (groups < 1 || W % groups != 0) return (int)cudaErrorInvalidValue;
+  const int Wg = W / groups;
+  const unsigned grid = (unsigned)(tokens * groups);
   CB_DISPATCH_FLOAT(dtype, T, {
-    const bool vec = W % 4 == 0 && ldy % 4 == 0 && ((uintptr_t)y % (4 * sizeof(T))) == 0 &&
+    const size_t ysz = y_f32 ? sizeof(float) : sizeof(T);
+    const bool vec = Wg % 4 == 0 && ldy % 4 == 0 && ((uintptr_t)y % (4 * ysz)) == 0 &&
                      ((uintptr_t)w % (4 * sizeof(T))) == 0 && ((uintptr_t)h % (4 * sizeof(T))) == 0 && ((uintptr_t)x % 16) == 0;
-    if (vec)
-      rmsnorm_residual_kernel<T, 4><<<(unsigned)tokens, 256, 0, st>>>(x, (const T*)y, ldy, (const T*)w, (T*)h, W, eps,
-                                                                     mult, offset);
-    else
-      rmsnorm_residual_kernel<T, 1><<<(unsigned)tokens, 256, 0, st>>>(x, (const T*)y, ldy, (const T*)w, (T*)h, W, eps,
-                                                                     mult, offset);
+    const int per = vec ? Wg / 4 : Wg;
+    const int threads = per >= 256 ? 256 : (per + 31) / 32 * 32;
+    if (y_f32) {
+      if (vec)
+        rmsnorm_residual_kernel<T, float, 4><<<grid, threads, 0, st>>>(x, (const float*)y, ldy, (const T*)w, (T*)h, W, groups,
+                                                                      eps, mult, offset);
+      else
+        rmsnorm_residual_kernel<T, float, 1><<<grid, threads, 0, st>>>(x, (const float*)y, ldy, (const T*)w, (T*)h, W, groups,
+                                                                      eps, mult, offset);
+    } else if (vec) {
+      rmsnorm_residual_kernel<T, T, 4><<<grid, threads, 0, st>>>(x, (const T*)y, ldy, (const T*)w, (T*)h, W, groups, eps,
+                                                                mult, offset);
+    } else {
+      rmsnorm_residual_kernel<T, T, 1><<<grid, threads, 0, st>>>(x, (const T*)y, ldy, (const T*)w, (T*)h, W, groups, eps,
+                                                                mult, offset);
+    }
   });
   return CB_LAUNCH_CHECK();
 }
 
-int cb_rmsnorm_f32in(const float* x, const void* w, void* out, int64_t tokens, int W, float eps, float offset, int dtype,
-                     cudaStream_t st) {
+int cb_rmsnorm_f32in(const float* x, int64_t ldx, const void* w, void* out, int64_t tokens, int W, int groups, float eps,
+                     float offset, int dtype, cudaStream_t st) {
+  if (tokens == 0) return 0;
+  if (groups < 1 || W % groups != 0) return (int)cudaErrorInvalidValue;
+  const int Wg = W / groups;
+  const int threads = Wg >= 256 ? 256 : (Wg + 31) / 32 * 32;
+  CB_DISPATCH_FLOAT(dtype, T, {
+    rmsnorm_f32in_kernel<T><<<(unsigned)(tokens * groups), threads, 0, st>>>(x, ldx, (const T*)w, (T*)out, W, groups, eps,
+                                                                            offset);
+  });
+  return CB_LAUNCH_CHECK();
+}
+
+int cb_depth_mix(const float* hist, int64_t stride, int n, const float* coef, float* out, void* h, int64_t total,
+                 int dtype, cudaStream_t st) {
+  if (total == 0) return 0;
+  if (total % 4 != 0 || stride % 4 != 0 || ((uintptr_t)hist % 16) != 0 || ((uintptr_t)out % 16) != 0)
+    return (int)cudaErrorInvalidValue;
+  const int64_t total4 = total / 4;
+  const unsigned grid = (unsigned)((total4 + 255) / 256 < 148 * 16 ? (total4 + 255) / 256 : 148 * 16);
+  CB_DISPATCH_FLOAT(dtype, T, { depth_mix_kernel<T><<<grid, 256, 0, st>>>(hist, stride, n, coef, out, (T*)h, total4); });
+  return CB_LAUNCH_CHECK();
+}
+
+int cb_poly_norm(const void* z, int64_t ldz, void* out, int64_t tokens, int F, const float* coef, float eps, int dtype,
+                 cudaStream_t st) {
   if (tokens == 0) return 0;
   CB_DISPATCH_FLOAT(dtype, T, {
-    rmsnorm_f32in_kernel<T><<<(unsigned)tokens, 256, 0, st>>>(x, (const T*)w, (T*)out, W, eps, offset);
+    poly_norm_kernel<T><<<(unsigned)tokens, 256, 0, st>>>((const T*)z, ldz, (T*)out, F, coef, eps);
+  });
+  return CB_LAUNCH_CHECK();
+}
+
+int cb_head_rmsnorm(const void* x, int64_t ldx, void* out, int64_t ldo, int64_t tokens, int heads, int heads_a, int dim,
+                    const void* wa, const void* wb, float eps, int dtype, cudaStream_t st) {
+  if (tokens == 0 || heads == 0) return 0;
+  const int64_t units = tokens * heads;
+  CB_DISPATCH_FLOAT(dtype, T, {
+    head_rmsnorm_kernel<T><<<(unsigned)((units + 3) / 4), 128, 0, st>>>((const T*)x, ldx, (T*)out, ldo, tokens, heads,
+                                                                       heads_a, dim, (const T*)wa, (const T*)wb, eps);
   });
   return CB_LAUNCH_CHECK();
 }
@@ -2095,8 +2252,8 @@ int cb_paged_kv_write_mix(const void* k, int64_t ldk, const void* v, int64_t ldv
 int cb_paged_bias_attention(const void* q, int64_t ldq, const void* k_cache, const void* v_cache, const int* block_tables,
                             const int* token_seq, const int* token_pos, const float* bias_table, const int* bucket_start,
                             int nbuckets, void* out, int64_t tokens, int heads, int kv_heads, int dim, int vdim, int ldv,
-                            int block_size, int max_blocks, float scale, int sink, int mask_block, int dtype,
-                            cudaStream_t st) {
+                            int block_size, int max_blocks, float scale, int sink, int mask_block, const float* sink_vals,
+                            const float* slopes, int window, int dtype, cudaStream_t st) {
   if (tokens == 0) return 0;
   if (vdim > 32 * ATT_MAX_VREG || heads % kv_heads != 0) return (int)cudaErrorInvalidValue;
   const int nwarps = 4;
@@ -2106,7 +2263,7 @@ int cb_paged_bias_attention(const void* q, int64_t ldq, const void* k_cache, con
     paged_bias_attention_kernel<T><<<(unsigned)((units + nwarps - 1) / nwarps), nwarps * 32, smem, st>>>(
         (const T*)q, ldq, (const T*)k_cache, (const T*)v_cache, block_tables, token_seq, token_pos, bias_table,
         bucket_start, nbuckets, (T*)out, tokens, heads, kv_heads, dim, vdim, ldv, block_size, max_blocks, scale, sink,
-        mask_block);
+        mask_block, sink_vals, slopes, window);
   });
   return CB_LAUNCH_CHECK();
 }
@@ -2118,8 +2275,8 @@ int cb_paged_bias_attention_mma(const void* q, int64_t ldq, const void* k_cache,
                                 const float* bias_table, const uint8_t* lut, int lut_n, int nbuckets, void* out,
                                 int64_t tokens, int nseq, int max_q, int heads, int kv_heads, int dim, int vdim, int ldv,
                                 int block_size, int max_blocks, float scale, int sink, int chunk, int max_splits,
-                                float* part_o, float* part_ml, int mask_block, int wide_weights, int dtype,
-                                cudaStream_t st) {
+                                float* part_o, float* part_ml, int mask_block, int wide_weights, const float* sink_vals,
+                                const float* slopes, int window, int dtype, cudaStream_t st) {
   if (nseq == 0 || max_q == 0) return 0;
   if (heads % kv_heads != 0 || dim % 8 != 0 || vdim % 8 != 0 || dim > 256 || vdim > 256 || (ldq & 7) || ((uintptr_t)q & 15) ||
       (ldv & 7) || ldv < vdim ||
@@ -2133,16 +2290,17 @@ int cb_paged_bias_attention_mma(const void* q, int64_t ldq, const void* k_cache,
     return launch_attention_mma<T, D, 1, true>(q, ldq, k_cache, v_cache, block_tables, cu_q, ctx_len, token_pos,       \
                                                bias_table, lut, lut_n, nbuckets, out, tokens, nseq, max_q, heads,      \
                                                kv_heads, dim, vdim, ldv, block_size, max_blocks, scale, sink, chunk,   \
-                                               max_splits, part_o, part_ml, mask_block, wide_weights, st);             \
+                                               max_splits, part_o, part_ml, mask_block, wide_weights, sink_vals,       \
+                                               slopes, window, st);                                                    \
   if (wide)                                                                                                           \
     return launch_attention_mma<T, D, 2>(q, ldq, k_cache, v_cache, block_tables, cu_q, ctx_len, token_pos, bias_table, \
                                          lut, lut_n, nbuckets, out, tokens, nseq, max_q, heads, kv_heads, dim, vdim,  \
                                          ldv, block_size, max_blocks, scale, sink, chunk, max_splits, part_o, part_ml, \
-                                         mask_block, wide_weights, st);                                               \
+                                         mask_block, wide_weights, sink_vals, slopes, window, st);                    \
   return launch_attention_mma<T, D, 1>(q, ldq, k_cache, v_cache, block_tables, cu_q, ctx_len, token_pos, bias_table,  \
                                        lut, lut_n, nbuckets, out, tokens, nseq, max_q, heads, kv_heads, dim, vdim,   \
                                        ldv, block_size, max_blocks, scale, sink, chunk, max_splits, part_o, part_ml,  \
-                                       mask_block, wide_weights, st)
+                                       mask_block, wide_weights, sink_vals, slopes, window, st)
   CB_DISPATCH_HALF(dtype, T, {
     if (dmax <= 32) { CB_ATT_MMA(T, 32); }
     else if (dmax <= 64) { CB_ATT_MMA(T, 64); }
@@ -2153,7 +2311,7 @@ int cb_paged_bias_attention_mma(const void* q, int64_t ldq, const void* k_cache,
       return launch_attention_mma<T, 256, 1>(q, ldq, k_cache, v_cache, block_tables, cu_q, ctx_len, token_pos, bias_table,
                                              lut, lut_n, nbuckets, out, tokens, nseq, max_q, heads, kv_heads, dim, vdim,
                                              ldv, block_size, max_blocks, scale, sink, chunk, max_splits, part_o, part_ml,
-                                             mask_block, wide_weights, st);
+                                             mask_block, wide_weights, sink_vals, slopes, window, st);
     }
   });
 #undef CB_ATT_MMA

@@ -425,7 +425,9 @@ inline EpParams make_ep(const void* const* rows, const void* const* flags, const
 template <typename T, int VEC>
 __global__ void __launch_bounds__(256) moe_gather_combine_kernel(const T* __restrict__ rows, const int64_t* __restrict__ row_of,
                                                                  const float* __restrict__ w, float* __restrict__ out,
-                                                                 int64_t tokens, int k, int H) {
+                                                                 int64_t tokens, int k, int H,
+                                                                 const T* __restrict__ extra, int64_t lde,
+                                                                 const float* __restrict__ extra_gate, int64_t ldg) {
   struct alignas(sizeof(T) * VEC) Pack { T v[VEC]; };
   const int per = H / VEC;
   const int64_t total = tokens * per;
@@ -440,6 +442,12 @@ __global__ void __launch_bounds__(256) moe_gather_combine_kernel(const T* __rest
       const Pack r = *reinterpret_cast<const Pack*>(rows + row_of[t * k + j] * H + c);
 #pragma unroll
       for (int e = 0; e < VEC; ++e) acc[e] = fmaf(wj, to_f32<T>(r.v[e]), acc[e]);
+    }
+    if (extra != nullptr) {        // a row that every token takes (shared expert), times sigmoid(extra_gate[t]) if given
+      const float ge = extra_gate != nullptr ? 1.f / (1.f + expf(-extra_gate[t * ldg])) : 1.f;
+      const Pack r = *reinterpret_cast<const Pack*>(extra + t * lde + c);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) acc[e] = fmaf(ge, to_f32<T>(r.v[e]), acc[e]);
     }
 #pragma unroll
     for (int e = 0; e < VEC; ++e) out[t * H + c + e] = acc[e];
@@ -609,15 +617,20 @@ int cb_moe_ep_combine(const int* topk_idx, const float* w, const int* pos, const
 }
 
 int cb_moe_gather_combine(const void* rows, const int64_t* row_of, const float* w, float* out, int tokens, int k, int H,
-                          int dtype, cudaStream_t st) {
+                          const void* extra, int64_t lde, const float* extra_gate, int64_t ldg, int dtype,
+                          cudaStream_t st) {
   if (tokens == 0) return 0;
   CB_DISPATCH_FLOAT(dtype, T, {
     constexpr int V = 16 / sizeof(T);
-    const bool vec = H % V == 0 && ((uintptr_t)rows & 15) == 0;
+    const bool vec = H % V == 0 && ((uintptr_t)rows & 15) == 0 && ((uintptr_t)extra & 15) == 0 && lde % V == 0;
     const int64_t total = (int64_t)tokens * (vec ? H / V : H);
     const unsigned grid = (unsigned)((total + 255) / 256 < 148 * 32 ? (total + 255) / 256 : 148 * 32);
-    if (vec) moe_gather_combine_kernel<T, V><<<grid, 256, 0, st>>>((const T*)rows, row_of, w, out, tokens, k, H);
-    else moe_gather_combine_kernel<T, 1><<<grid, 256, 0, st>>>((const T*)rows, row_of, w, out, tokens, k, H);
+    if (vec)
+      moe_gather_combine_kernel<T, V><<<grid, 256, 0, st>>>((const T*)rows, row_of, w, out, tokens, k, H, (const T*)extra,
+                                                           lde, extra_gate, ldg);
+    else
+      moe_gather_combine_kernel<T, 1><<<grid, 256, 0, st>>>((const T*)rows, row_of, w, out, tokens, k, H, (const T*)extra,
+                                                           lde, extra_gate, ldg);
   });
   return CB_LAUNCH_CHECK();
 }

@@ -60,12 +60,23 @@ class MixerSpec:
                        multiplied by a tanh-GELU branch.
     kind "pair":       several mixers side by side that read the same input (`parts`); every part's output is RMS-normed
                        over the model width with a weight of its own and the results are averaged.
+    kind "delta":      gated delta rule with ONE decay per head, exp(-exp(A_log) softplus(W_a h + dt_bias)), a write
+                       strength sigmoid(W_b h), short causal convolutions of `conv` taps + silu on q, k, v, unit-length
+                       q / k, the read-out brought to unit RMS per head, weighted and gated by silu(W_g h).
+
+    kind "latent" also takes: `q_rank` (queries through an RMS-normalised latent of that width), `window`,
+    `sink_learned`, `rot_scaling`.
 
     kind "attention" also takes: rotary positions on the first `rot_dims` channels of every q / k head (pairs (2i, 2i + 1)
     when `rot_interleaved`, else (i, i + rot_dims / 2)); `head_unit_norm` (q and k divided by their root mean square over
     the head, after the rotation, no weight); `mask_block` (a position sees only the keys of its own block of that many
     positions, counted from the start of the sequence); `out_gate` (heads times sigmoid(W_g x) before the output
-    projection)."""
+    projection); `conv` (a causal convolution of that many taps on every channel of the q and k projections, no
+    activation; its last inputs are carried like a recurrent state); `head_norm` (RMS norm of every q / k head with one
+    weight over the head's channels per projection); `values_from_keys` (no value projection: the values are the keys as
+    they leave the convolution, before any norm); `dist_slopes` (score minus 2^(-8 (h + 1) / heads) x distance);
+    `window` (a position sees itself and the window - 1 positions before it); `sink_learned` (the sink's score is a
+    learned number per head instead of 0)."""
 
     kind: str = "attention"
     heads: int = 1
@@ -99,6 +110,13 @@ class MixerSpec:
     lru_width: int = 0                # rglru: channels
     blocks: int = 1                   # rglru: blocks of the gate matrices
     lru_c: float = 8.0                # rglru: decay = exp(-lru_c * r * softplus(lam))
+    q_rank: int = 0                   # latent: width of the normalised query latent (0 = queries straight from the input)
+    window: int = 0                   # attention / latent: > 0 keeps the keys pos - window + 1 .. pos
+    sink_learned: bool = False        # the softmax sink's score is a learned number per head (implies a sink)
+    rot_scaling: Optional[List[float]] = None     # (factor, original length, fast, slow): stretched slow frequencies
+    head_norm: bool = False           # attention: RMS norm per q / k head with a weight shared by the heads
+    values_from_keys: bool = False    # attention: values = keys before their norm (no value projection)
+    dist_slopes: bool = False         # attention: score -= 2^(-8 (h + 1) / heads) * (query position - key position)
     parts: Optional[List["MixerSpec"]] = None      # pair: the mixers that run side by side
 
     def __post_init__(self) -> None:
@@ -116,7 +134,9 @@ class MixerSpec:
     def recurrent(self) -> bool:
         if self.kind == "pair":
             return any(p.recurrent for p in self.parts)
-        return self.kind in ("lightning", "channel_delta", "retention", "mlstm", "ssd", "rglru")
+        if self.kind == "attention":                  # a convolution in front of attention carries its last inputs
+            return self.conv > 0
+        return self.kind in ("lightning", "channel_delta", "retention", "mlstm", "ssd", "rglru", "delta")
 
     @property
     def paged(self) -> bool:
@@ -142,7 +162,10 @@ class MixerSpec:
 class ExpertFFSpec:
     """Routed feed-forward of one layer: `experts` gated experts of width `ff`, every token uses the `top` of largest
     softmax score (weights renormalised to one), plus an optional shared expert of width `shared_ff` for every token.
-    Expert activation: g = min(gate, limit), u = clamp(up, -limit, limit), y = g * sigmoid(alpha * g) * (u + 1)."""
+    Expert activation `act`: "clamped": g = min(gate, limit), u = clamp(up, -limit, limit),
+    y = g * sigmoid(alpha * g) * (u + 1); "silu": y = silu(gate) * up.  `shared_gate`: the shared expert's output is
+    multiplied by sigmoid(w_sg . h), one number per token.  (Softmax over all experts renormalised over the chosen ones
+    equals the softmax over the chosen logits alone.)"""
 
     experts: int = 1
     top: int = 1
@@ -151,6 +174,8 @@ class ExpertFFSpec:
     alpha: float = 1.702
     shared_ff: int = 0
     shared_limit: float = 7.0
+    act: str = "clamped"
+    shared_gate: bool = False
 
 
 @dataclass
@@ -158,6 +183,8 @@ class LayerSpec:
     mixer: MixerSpec = field(default_factory=MixerSpec)
     ff: Optional[int] = None          # dense feed-forward width; None = no dense feed-forward
     moe: Optional[ExpertFFSpec] = None  # routed feed-forward instead of a dense one
+    ff_act: Optional[str] = None      # dense feed-forward: activation of this layer instead of `ModelConfig.hidden_act`
+                                      # ("polynorm": learned mix of the first three powers, each brought to unit RMS)
 
     def __post_init__(self) -> None:
         if isinstance(self.mixer, dict):
@@ -221,6 +248,9 @@ class ModelConfig:
     norm_bias: bool = True            # layer norms carry a bias
     logit_softcap: Optional[float] = None   # logits <- cap * tanh(logits / cap), after `logit_scale`
     fp32_logits: bool = False         # 16-bit serving keeps the LM head's fp32 accumulator (no 16-bit rounding of logits)
+    norm_groups: int = 1              # "sublayer_out" norms and the final norm: RMS over each of this many equal parts
+    depth_average: bool = False       # what a layer hands on is a learned weighted sum of the embedding output and of
+                                      # all layer results so far (one weight vector per layer)
     # looped span: layers loop_start .. loop_stop-1 run `loop_times` times in a row with the same weights; every pass
     # has caches / states of its own and starts by adding the embedding output (not the first pass) and a learned
     # vector of the pass to the stream

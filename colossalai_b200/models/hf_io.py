@@ -41,6 +41,10 @@ def config_from_hf(hf: dict) -> ModelConfig:
         from .pogorax import pogorax_config
 
         return pogorax_config(hf)
+    if hf.get("architecture") == "Domorax":
+        from .domorax import domorax_config
+
+        return domorax_config(hf)
     if mt == "gpt2":
         return ModelConfig(model_type="gpt2", vocab_size=hf["vocab_size"], hidden_size=hf["n_embd"],
                            intermediate_size=hf.get("n_inner") or 4 * hf["n_embd"], num_hidden_layers=hf["n_layer"],
@@ -496,6 +500,10 @@ def load_hf_checkpoint(path: str, dtype: torch.dtype = torch.bfloat16, device: s
         from .pogorax import load_pogorax
 
         return load_pogorax(path, hf_cfg, dtype, device)
+    if hf_cfg.get("architecture") == "Domorax":
+        from .domorax import load_domorax
+
+        return load_domorax(path, hf_cfg, dtype, device)
     cfg = config_from_hf(hf_cfg)
     model = build_model(cfg).to(dtype)
     merged: Dict[str, torch.Tensor] = {}

@@ -11,11 +11,14 @@
   * `MatrixLSTM`: matrix memory with exponential input / forget gates, a running maximum and a normaliser vector;
   * `SelectiveStateSpace`: state space with input-dependent step sizes behind a causal convolution, gate before the norm;
   * `GatedLinearRecurrence`: per-channel real-gated linear recurrent unit behind a causal convolution, times a GELU branch;
-  * `MixerPair`: mixers side by side on the same input; their RMS-normed outputs are averaged.
+  * `MixerPair`: mixers side by side on the same input; their RMS-normed outputs are averaged;
+  * `DeltaMixer`: gated delta rule with one decay per head behind short causal convolutions, gated unit-RMS read-out.
 
 `BiasSinkAttention` also covers plain paged softmax attention with rotary positions (half or interleaved pairs, on a part
-of the head), a weightless unit norm of q / k heads, a block mask (a position sees its own block of positions only) and a
-sigmoid output gate: every one of these is a field of the `MixerSpec`.
+of the head), a weightless unit norm of q / k heads, a block mask (a position sees its own block of positions only), a
+sigmoid output gate, a short convolution on q | k, an RMS norm per q / k head with a shared weight, values taken from the
+keys, a linear distance penalty per head, a sliding window and a learned sink score: every one of these is a field of the
+`MixerSpec`.
 
 Every mixer keeps the call signature of `Attention` (`forward(x, meta, rope, kv_cache)`) and is selected per layer by
 `ModelConfig.layer_specs[i].mixer.kind` (`build_mixer`).  `kv_cache` is the step runtime (`inference.modeling.PagedKVRuntime`):
@@ -35,7 +38,7 @@ from ..ops import mixers as mops
 from .config import MixerSpec, ModelConfig
 
 __all__ = ["BiasSinkAttention", "LightningAttention", "ChannelDeltaMixer", "LatentAttention", "Retention", "MatrixLSTM",
-           "SelectiveStateSpace", "GatedLinearRecurrence", "MixerPair", "build_mixer"]
+           "SelectiveStateSpace", "GatedLinearRecurrence", "MixerPair", "DeltaMixer", "build_mixer"]
 
 
 class _MixerBase(nn.Module):
@@ -62,9 +65,20 @@ class BiasSinkAttention(_MixerBase):
         super().__init__(cfg, spec, layer_idx)
         H, G, d, dv = spec.heads, spec.kv_heads, spec.dim, spec.vdim
         assert spec.rot_dims % 2 == 0 and spec.rot_dims <= d
-        # q | k | v (| output gate): one GEMM reads the layer input
-        self.qkv_proj = nn.Linear(cfg.hidden_size, H * d + G * d + G * dv + (H * dv if spec.out_gate else 0),
+        assert not spec.values_from_keys or (dv == d and not spec.v_mix), "values taken from the keys are key-wide"
+        assert not (spec.conv and (spec.rot_dims or spec.head_unit_norm or spec.proj_norm)), \
+            "the convolution on q | k is followed by the per-head norm only"
+        # q | k | v (| output gate): one GEMM reads the layer input (no v with `values_from_keys`)
+        self.v_width = 0 if spec.values_from_keys else G * dv
+        self.qkv_proj = nn.Linear(cfg.hidden_size, H * d + G * d + self.v_width + (H * dv if spec.out_gate else 0),
                                   bias=spec.bias)
+        if spec.conv:
+            self.conv_weight = nn.Parameter(torch.zeros((H + G) * d, spec.conv))       # q channels, then k channels
+        if spec.head_norm:
+            self.q_head_norm_weight = nn.Parameter(torch.ones(d))
+            self.k_head_norm_weight = nn.Parameter(torch.ones(d))
+        if spec.sink_learned:
+            self.sink_logit = nn.Parameter(torch.zeros(H))
         if spec.proj_norm:
             self.q_norm_weight = nn.Parameter(torch.ones(H * d))
             self.k_norm_weight = nn.Parameter(torch.ones(G * d))
@@ -79,7 +93,17 @@ class BiasSinkAttention(_MixerBase):
         sp, eps = self.spec, self.cfg.norm_eps
         H, G, d, dv = sp.heads, sp.kv_heads, sp.dim, sp.vdim
         qkv = self.qkv_proj(x)
-        q, k, v, gate = qkv.split([H * d, G * d, G * dv, H * dv if sp.out_gate else 0], dim=-1)
+        q, k, v, gate = qkv.split([H * d, G * d, self.v_width, H * dv if sp.out_gate else 0], dim=-1)
+        if sp.conv:
+            # the convolution comes directly after the projection; its window of last inputs lives in the layer's slot
+            qk = mops.short_conv_silu(qkv[:, : (H + G) * d], self.conv_weight, kv_cache.layer_state(self.layer_idx)["conv"],
+                                      kv_cache.ragged, activation=False)
+            q, k = qk[:, : H * d], qk[:, H * d:]
+        if sp.values_from_keys:
+            v = k                                          # as they leave the convolution, before the norm
+        if sp.head_norm:
+            qk = mops.head_rms_norm(qk if sp.conv else qkv, H, G, d, self.q_head_norm_weight, self.k_head_norm_weight, eps)
+            q, k = qk[:, : H * d], qk[:, H * d:]
         if sp.rot_dims or sp.head_unit_norm:
             # q and k heads sit side by side in the projection: rotated and normalised in place, in one launch
             table = mops.rotary_table(kv_cache.max_len_host, sp.rot_dims, sp.rot_base, x.device) if sp.rot_dims else None
@@ -103,9 +127,12 @@ class BiasSinkAttention(_MixerBase):
                 mops.log_bucket_starts(sp.bias_buckets, sp.bias_max), dtype=torch.int32))
             lut = self._aux("lut", x.device, lambda: mops.bucket_lut(
                 mops.log_bucket_starts(sp.bias_buckets, sp.bias_max)))
+        sinks = self._aux("sink", x.device, lambda: self.sink_logit.detach().float()) if sp.sink_learned else None
+        slopes = self._aux("slopes", x.device, lambda: mops.distance_slopes(H)) if sp.dist_slopes else None
         o = kv_cache.attend_ragged(self.layer_idx, q, k, v, self.scale, bias_table=table, bucket_starts=starts,
-                                   sink=sp.sink, v_other=v_other, lam=lam, lut=lut, mask_block=sp.mask_block,
-                                   wide_weights=sp.wide_weights)
+                                   sink=sp.sink or sp.sink_learned, v_other=v_other, lam=lam, lut=lut,
+                                   mask_block=sp.mask_block, wide_weights=sp.wide_weights, sink_values=sinks,
+                                   slopes=slopes, window=sp.window)
         if sp.out_gate:
             o = mops.sigmoid_gate_mul(o, gate)
         return self.o_proj(o)
@@ -165,6 +192,41 @@ class ChannelDeltaMixer(_MixerBase):
         return self.o_proj(o)
 
 
+class DeltaMixer(_MixerBase):
+    """Gated delta rule with one decay per head.  W_in h = [q | k | v | write strength | decay | gate]; q | k | v pass a
+    causal convolution and silu; q, k become unit vectors per head (q also times dim^-1/2); per token and head
+    g = exp(-exp(A_log) softplus(a + dt_bias)), beta = sigmoid(b): S <- g S; u = beta (v - S^T k); S <- S + k u^T;
+    o = S^T q.  S [dim, vdim] is zero at the start of a sequence and carried in fp32 together with the convolution's last
+    inputs.  Every head's o is divided by its root mean square, multiplied by a weight over vdim that the heads share and
+    by silu(W_g h), and projected."""
+
+    def __init__(self, cfg: ModelConfig, spec: MixerSpec, layer_idx: int) -> None:
+        super().__init__(cfg, spec, layer_idx)
+        H, G, d, dv = spec.heads, spec.kv_heads, spec.dim, spec.vdim
+        self.conv_channels = 2 * G * d + H * dv
+        self.in_proj = nn.Linear(cfg.hidden_size, self.conv_channels + 2 * H + H * dv, bias=False)
+        self.conv_weight = nn.Parameter(torch.zeros(self.conv_channels, max(spec.conv, 1)))
+        self.A_log = nn.Parameter(torch.zeros(H))
+        self.dt_bias = nn.Parameter(torch.zeros(H))
+        self.norm_weight = nn.Parameter(torch.ones(dv))
+        self.o_proj = nn.Linear(H * dv, cfg.hidden_size, bias=False)
+
+    def forward(self, x: torch.Tensor, meta, rope=None, kv_cache=None) -> torch.Tensor:
+        sp = self.spec
+        H, G, d, dv = sp.heads, sp.kv_heads, sp.dim, sp.vdim
+        z = self.in_proj(x)
+        qkv, b, a, gate = z.split([self.conv_channels, H, H, H * dv], dim=-1)
+        st = kv_cache.layer_state(self.layer_idx)
+        ragged = kv_cache.ragged
+        qkv = mops.short_conv_silu(qkv, self.conv_weight, st["conv"], ragged)
+        q, k, v = qkv.split([G * d, G * d, H * dv], dim=-1)
+        a_log = self._aux("A_log", x.device, lambda: self.A_log.detach().float())
+        dt_bias = self._aux("dt_bias", x.device, lambda: self.dt_bias.detach().float())
+        o = mops.state_scan_delta(q, k, v, a, b, a_log, dt_bias, st["S"], ragged, H, G, d, dv, head_decay=True)
+        o = mops.gated_group_rms_norm(o, self.norm_weight, gate, dv, self.cfg.norm_eps, x.dtype, gate_act="silu")
+        return self.o_proj(o)
+
+
 class LatentAttention(_MixerBase):
     """q = W_q h, per head [dim unrotated | rot_dim rotated]; W_dkv h = [kv_rank latent | rot_dim key part]; the latent is
     RMS-normalised (weight `dkv_norm_weight`) -> c, the key part is rotated -> k_r (one for all heads).  Head n scores
@@ -174,13 +236,24 @@ class LatentAttention(_MixerBase):
     q_n . (U_n c) = (U_n^T q_n) . c, and sum_j p_j V_n c_j = V_n (sum_j p_j c_j), so the step runs multi-query attention
     with queries [U_n^T q_n | rotated q_r] against the cached rows, values = the rows' latent columns, and maps the
     `kv_rank`-wide results through V_n afterwards (two batched GEMMs over the heads).  A prompt, a portion and a decoded
-    token take the same path, so a position's result does not depend on how the prompt was cut."""
+    token take the same path, so a position's result does not depend on how the prompt was cut.
+
+    Options of the spec: `q_rank` > 0 - the queries come through a latent of their own, q = W_uq (rms(W_dq h) w_dq) (the
+    down-projection shares the GEMM that reads the layer input); `window` - a position sees the last `window` positions;
+    `sink_learned` - a learned score per head joins the softmax's denominator; `rot_scaling` - stretched rotary
+    frequencies (`ops.mixers.rotary_frequencies`)."""
 
     def __init__(self, cfg: ModelConfig, spec: MixerSpec, layer_idx: int) -> None:
         super().__init__(cfg, spec, layer_idx)
         H, d, r, dv, R = spec.heads, spec.dim, spec.rot_dim, spec.vdim, spec.kv_rank
         assert spec.rot_dims in (0, r) and r % 2 == 0, "the decoupled key part is rotated as a whole"
-        self.in_proj = nn.Linear(cfg.hidden_size, H * (d + r) + R + r, bias=False)       # q | latent | key part
+        self.q_width = spec.q_rank or H * (d + r)
+        self.in_proj = nn.Linear(cfg.hidden_size, self.q_width + R + r, bias=False)      # q (or its latent) | latent | key part
+        if spec.q_rank:
+            self.dq_norm_weight = nn.Parameter(torch.ones(spec.q_rank))
+            self.uq_proj = nn.Linear(spec.q_rank, H * (d + r), bias=False)
+        if spec.sink_learned:
+            self.sink_logit = nn.Parameter(torch.zeros(H))
         self.dkv_norm_weight = nn.Parameter(torch.ones(R))
         self.uk = nn.Parameter(torch.empty(H, d, R))              # U_n: latent -> unrotated key of head n
         self.uv = nn.Parameter(torch.empty(H, dv, R))             # V_n: latent -> value of head n
@@ -194,16 +267,21 @@ class LatentAttention(_MixerBase):
         H, d, r, dv, R = sp.heads, sp.dim, sp.rot_dim, sp.vdim, sp.kv_rank
         T = x.shape[0]
         z = self.in_proj(x)
-        q, dkv = z[:, : H * (d + r)], z[:, H * (d + r):]
+        q, dkv = z[:, : self.q_width], z[:, self.q_width:]
+        if sp.q_rank:
+            q = self.uq_proj(mops.head_rms_norm(q, 1, 0, sp.q_rank, self.dq_norm_weight, None, self.cfg.norm_eps))
         ragged = kv_cache.ragged
-        table = mops.rotary_table(kv_cache.max_len_host, r, sp.rot_base, x.device)
+        table = mops.rotary_table(kv_cache.max_len_host, r, sp.rot_base, x.device, sp.rot_scaling)
         mops.latent_kv_write(dkv, self.dkv_norm_weight, self.cfg.norm_eps, R, table, kv_cache.latent_cache(self.layer_idx),
                              kv_cache.block_tables, ragged)
         qa = torch.empty(T, H * (R + r), dtype=x.dtype, device=x.device)
         qa3 = qa.view(T, H, R + r)
         torch.bmm(q.view(T, H, d + r)[..., :d].transpose(0, 1), self.uk, out=qa3[..., :R].transpose(0, 1))
         mops.rotary_half(q, qa, H, d + r, d, R + r, R, r, r, table, ragged.token_pos)
-        o = kv_cache.attend_latent(self.layer_idx, qa, self.scale, R)                  # [T, H x R]
+        sinks = self._aux("sink", x.device, lambda: self.sink_logit.detach().float()) if sp.sink_learned else None
+        o = kv_cache.attend_latent(self.layer_idx, qa, self.scale, R, window=sp.window,
+                                   sink=sp.sink or sp.sink_learned, sink_values=sinks,
+                                   wide_weights=sp.wide_weights)                              # [T, H x R]
         o = torch.bmm(o.view(T, H, R).transpose(0, 1), self.uv.transpose(1, 2))        # [H, T, dv]
         return self.o_proj(o.transpose(0, 1).reshape(T, H * dv))
 
@@ -361,7 +439,7 @@ class MixerPair(nn.Module):
 
 _KINDS = {"attention": BiasSinkAttention, "lightning": LightningAttention, "channel_delta": ChannelDeltaMixer,
           "latent": LatentAttention, "retention": Retention, "mlstm": MatrixLSTM, "ssd": SelectiveStateSpace,
-          "rglru": GatedLinearRecurrence, "pair": MixerPair}
+          "rglru": GatedLinearRecurrence, "pair": MixerPair, "delta": DeltaMixer}
 
 
 def _build(cfg: ModelConfig, spec: MixerSpec, layer_idx: int) -> nn.Module:

@@ -192,27 +192,48 @@ class ClampedGLU(nn.Module):
         return self.down_proj(ops.clamped_glu(self.gate_up_proj(x), self.limit, self.alpha))
 
 
+class SiluGLU(nn.Module):
+    """Gated feed-forward without biases: y = W_down (silu(W_gate h) * (W_up h)); gate and up share one GEMM."""
+
+    def __init__(self, cfg: ModelConfig, intermediate: int) -> None:
+        super().__init__()
+        self.gate_up_proj = nn.Linear(cfg.hidden_size, 2 * intermediate, bias=False)
+        self.down_proj = nn.Linear(intermediate, cfg.hidden_size, bias=False)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return self.down_proj(ops.glu(self.gate_up_proj(x), "silu"))
+
+
 class ClampedExpertFF(nn.Module):
     """Routed feed-forward of a hybrid decoder layer (`LayerSpec.moe`): router scores = softmax over ALL experts in fp32,
     the `top` largest are used with their scores renormalised to one (+ 1e-20 in the divisor); experts and the optional
     shared expert are `ClampedGLU`s without biases.  The routed part runs as two grouped GEMMs over the token rows sorted
     by expert and is combined in fp32 by a gather in a fixed order (row j of a token is its j-th choice), so a token's
     result does not depend on what else is in the batch.  `forward` returns (routed sum fp32, shared output or None):
-    the caller adds both to the fp32 residual stream."""
+    the caller adds both to the fp32 residual stream.
+
+    `spec.act == "silu"`: the experts are plain `silu(gate) * up` units.  `spec.shared_gate`: the shared expert's output
+    is multiplied by sigmoid(w_sg . h) per token - w_sg is the router matrix's last row, so the gate's logit comes out of
+    the router's fp32 product - and joins the routed rows in the fp32 gather; `forward` then returns that one fp32 sum."""
 
     def __init__(self, cfg: ModelConfig, spec) -> None:
         super().__init__()
         self.cfg, self.spec = cfg, spec
-        self.router = nn.Linear(cfg.hidden_size, spec.experts, bias=False)
+        assert spec.act in ("clamped", "silu") and not (spec.shared_gate and not spec.shared_ff)
+        self.router = nn.Linear(cfg.hidden_size, spec.experts + int(spec.shared_gate), bias=False)
         self.experts = GroupedExperts(cfg, spec.experts, spec.ff, gated_act=self._act)
         if spec.shared_ff:
-            self.shared = ClampedGLU(cfg, spec.shared_ff, spec.shared_limit, spec.alpha)
+            self.shared = SiluGLU(cfg, spec.shared_ff) if spec.act == "silu" else \
+                ClampedGLU(cfg, spec.shared_ff, spec.shared_limit, spec.alpha)
         self.shard_config = None
 
     def _act(self, h: torch.Tensor, valid_rows) -> torch.Tensor:
+        if self.spec.act == "silu":
+            return ops.glu(h, "silu", valid_rows=valid_rows if h.is_cuda else None)
         return ops.clamped_glu(h, self.spec.limit, self.spec.alpha, valid_rows=valid_rows if h.is_cuda else None)
 
-    def route(self, x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    def route(self, x: torch.Tensor):
+        """(weights fp32 [T, top], experts [T, top], the shared expert's gate logit fp32 [T] or None)."""
         from ..ops.moe import router_topk
 
         if x.is_cuda and x.dtype != torch.float32 and self.router.weight.dtype == x.dtype:
@@ -220,16 +241,22 @@ class ClampedExpertFF(nn.Module):
             logits = torch.mm(x, self.router.weight.t(), out_dtype=torch.float32)
         else:
             logits = F.linear(x.float(), self.router.weight.float())
+        sg = None
+        if self.spec.shared_gate:
+            logits, sg = logits[:, : self.spec.experts], logits[:, self.spec.experts]
         if x.dtype == torch.float32:            # 32-bit serving: IEEE exponentials
             p = torch.softmax(logits, -1)
             w, idx = torch.topk(p, self.spec.top, dim=-1)
-            return w / (w.sum(-1, keepdim=True) + 1e-20), idx
-        return router_topk(logits, self.spec.top, renormalize=True)
+            return w / (w.sum(-1, keepdim=True) + 1e-20), idx, sg
+        return router_topk(logits, self.spec.top, renormalize=True) + (sg,)
 
-    def forward(self, x: torch.Tensor) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+    def forward(self, x: torch.Tensor):
         from ..moe import dispatch_combine
 
         x2 = x.reshape(-1, x.shape[-1])
-        w, idx = self.route(x2)
+        w, idx, sg = self.route(x2)
+        if self.spec.shared_gate:
+            return dispatch_combine.moe_forward_gather(x2, w, idx, self.experts, self.spec.experts,
+                                                       extra=self.shared(x2), extra_gate=sg)
         routed = dispatch_combine.moe_forward_gather(x2, w, idx, self.experts, self.spec.experts)
         return routed, (self.shared(x2) if self.spec.shared_ff else None)

@@ -307,20 +307,39 @@ class MLAttention(nn.Module):
 
 
 class MLP(nn.Module):
-    def __init__(self, cfg: ModelConfig, intermediate_size: Optional[int] = None) -> None:
+    """Dense feed-forward.  `act` overrides the config's activation for this layer; "polynorm" is the non-gated unit
+    W_down (a N(z) + b N(z^2) + c N(z^3) + e) with z = W_up h, powers taken element by element, N the division of a token's
+    vector by its root mean square, and (a, b, c, e) = `act_coef` learned per layer."""
+
+    def __init__(self, cfg: ModelConfig, intermediate_size: Optional[int] = None, act: Optional[str] = None) -> None:
         super().__init__()
         self.cfg = cfg
         inter = intermediate_size or cfg.intermediate_size
         self.intermediate_size = inter
-        if cfg.glu:
+        self.act = act or cfg.hidden_act
+        if self.act == "polynorm":
+            self.up_proj = nn.Linear(cfg.hidden_size, inter, bias=False)
+            self.act_coef = nn.Parameter(torch.tensor([1.0, 0.0, 0.0, 0.0]))
+            self._coef32: Dict[str, torch.Tensor] = {}
+        elif cfg.glu:
             self.gate_up_proj = nn.Linear(cfg.hidden_size, 2 * inter, bias=cfg.mlp_bias)
         else:
             self.up_proj = nn.Linear(cfg.hidden_size, inter, bias=cfg.mlp_bias)
         self.down_proj = nn.Linear(inter, cfg.hidden_size, bias=cfg.mlp_bias)
         self.shard_config = None
 
+    def _apply(self, fn, *a, **k):
+        if self.act == "polynorm":
+            self._coef32 = {}
+        return super()._apply(fn, *a, **k)
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        if self.cfg.glu:
+        if self.act == "polynorm":
+            key = str(x.device)
+            if key not in self._coef32:                   # the four numbers in fp32 on the device, built once
+                self._coef32[key] = self.act_coef.detach().float().contiguous()
+            h = ops.mixers.poly_norm(self.up_proj(x), self._coef32[key], self.cfg.norm_eps)
+        elif self.cfg.glu:
             h = ops.glu(self.gate_up_proj(x), self.cfg.hidden_act)
         else:
             up = self.up_proj
@@ -356,14 +375,29 @@ class DecoderLayer(nn.Module):
 
             self.mlp = ClampedExpertFF(cfg, spec.moe)
         elif spec is not None:
-            self.mlp = MLP(cfg, spec.ff) if spec.ff is not None else None
+            self.mlp = MLP(cfg, spec.ff, act=spec.ff_act) if spec.ff is not None else None
         elif moe is not None and layer_idx >= moe.first_k_dense_replace and (layer_idx % moe.moe_layer_freq == 0):
             from .moe import SparseMoE
 
             self.mlp = SparseMoE(cfg)
         else:
             self.mlp = MLP(cfg)
+        if cfg.depth_average:
+            # weights of the embedding output and of the results of layers 0 .. layer_idx in what this layer hands on
+            self.depth_weight = nn.Parameter(torch.cat([torch.zeros(layer_idx + 1), torch.ones(1)]))
         self.shard_config = None
+
+    def _apply(self, fn, *a, **k):          # parameters moved or cast: the fp32 copy of the depth weights is rebuilt
+        self.__dict__.pop("_depth_coef32", None)
+        return super()._apply(fn, *a, **k)
+
+    def depth_coef(self, device) -> torch.Tensor:
+        """`depth_weight` in fp32 on the compute device (built once per device)."""
+        cache = self.__dict__.setdefault("_depth_coef32", {})
+        key = str(device)
+        if key not in cache:
+            cache[key] = self.depth_weight.detach().float().contiguous().to(device)
+        return cache[key]
 
     def forward(self, x: torch.Tensor, meta: SeqMeta, rope=None, kv_cache=None) -> torch.Tensor:
         cfg = self.cfg
@@ -423,8 +457,10 @@ class DecoderLayer(nn.Module):
 
     def _forward_sublayer_out(self, x: torch.Tensor, meta: SeqMeta, rope, kv_cache) -> torch.Tensor:
         """x <- x + m * norm(mixer(x)); x <- x + m * norm(ff(x)): the sublayers read the stream itself and only their
-        output is normalised.  With an fp32 stream one kernel normalises, scales, adds and writes the compute-dtype copy
-        the next GEMM reads (`meta.stream_cast`)."""
+        output is normalised (over the whole row, or over each of `norm_groups` equal parts of it).  With an fp32 stream
+        one kernel normalises, scales, adds and writes the compute-dtype copy the next GEMM reads (`meta.stream_cast`).
+        A routed feed-forward hands its fp32 sum over as it is.  With `depth_average` the backbone mixes the layer
+        results afterwards and makes the next layer's copy itself."""
         cfg = self.cfg
         dt = self.input_layernorm.weight.dtype
         fp32_stream = x.dtype == torch.float32 and cfg.fp32_residual
@@ -432,12 +468,15 @@ class DecoderLayer(nn.Module):
             x = x.float()
         h = meta.stream_cast if (fp32_stream and meta.stream_cast is not None) else x.to(dt)
         y = self.self_attn(h, meta, rope, kv_cache)
-        h = ops.rms_norm_residual(x, y, self.input_layernorm.weight, cfg.norm_eps, cfg.residual_mult,
-                                  cfg.norm_weight_offset)
+        kw = dict(mult=cfg.residual_mult, offset=cfg.norm_weight_offset, groups=cfg.norm_groups)
+        last_cast = not (cfg.depth_average and fp32_stream)
+        h = ops.rms_norm_residual(x, y, self.input_layernorm.weight, cfg.norm_eps,
+                                  want_cast=self.mlp is not None or last_cast, **kw)
         if self.mlp is not None:
             y = self.mlp(h)
-            h = ops.rms_norm_residual(x, y, self.post_attention_layernorm.weight, cfg.norm_eps, cfg.residual_mult,
-                                      cfg.norm_weight_offset)
+            if isinstance(y, tuple):
+                y = y[0] if y[1] is None else y[0] + y[1].float()
+            h = ops.rms_norm_residual(x, y, self.post_attention_layernorm.weight, cfg.norm_eps, want_cast=last_cast, **kw)
         if fp32_stream:
             meta.stream_cast = h
             return x
@@ -619,6 +658,9 @@ class TransformerModel(nn.Module):
         start, end = self.layer_range()
         n_ckpt = self._num_ckpt_layers(end - start) if self.training else 0
         stream = cfg.fp32_residual and cfg.norm_placement == "pre" and not cfg.post_norm
+        if cfg.depth_average:
+            assert sm is None and not cfg.looped, "depth-averaged streams are not split over pipeline stages or looped"
+            return self._forward_depth_average(x, meta, rope, kv_cache)
         if cfg.looped or stream:
             # a span of layers may run several times with the same weights: every layer RUN has its own cache / state
             # (the runtime is told which), and every pass starts by adding the embedding output (not the first) and the
@@ -659,9 +701,36 @@ class TransformerModel(nn.Module):
                     x = layer(x, meta, rope, kv_cache)
         if last and cfg.final_norm:
             if cfg.fp32_residual and x.dtype == torch.float32:
-                x = ops.rms_norm_f32in(x, self.norm.weight, cfg.norm_eps, cfg.norm_weight_offset)
+                x = ops.rms_norm_f32in(x, self.norm.weight, cfg.norm_eps, cfg.norm_weight_offset, groups=cfg.norm_groups)
             else:
                 x = self.norm(x)
+        return x
+
+
+    def _forward_depth_average(self, x: torch.Tensor, meta: SeqMeta, rope, kv_cache) -> torch.Tensor:
+        """Layers on an fp32 stream whose results are all kept: with X_0 the embedding output and X_(i+1) the result of
+        layer i, layer i + 1 reads sum_(j <= i+1) a_i[j] X_j (a_i = layer i's `depth_weight`), and the final norm reads
+        the last such sum.  The history lives in one buffer [layers + 2, T, W]: slice i + 1 first holds layer i's input
+        and becomes its result (the layer updates the stream in place); the mixing kernel writes the next slice and the
+        compute-dtype copy the next layer's GEMMs read."""
+        cfg = self.cfg
+        n = len(self.layers)
+        T, W = x.shape
+        dt = self.norm.weight.dtype if cfg.final_norm else self.embed_tokens.weight.dtype
+        hist = torch.empty(n + 2, T, W, dtype=torch.float32, device=x.device)
+        hist[0].copy_(x)
+        hist[1].copy_(x)
+        meta.stream_cast = None
+        for i, layer in enumerate(self.layers):
+            layer(hist[i + 1], meta, rope, kv_cache)
+            meta.stream_cast = ops.mixers.depth_mix(hist, i + 2, layer.depth_coef(x.device), hist[i + 2],
+                                                    cast_dtype=dt if i + 1 < n else None)
+            if self.stream_trace is not None:
+                self.stream_trace.append(hist[i + 2].detach().clone())
+        x = hist[n + 1]
+        meta.stream_cast = None
+        if cfg.final_norm:
+            return ops.rms_norm_f32in(x, self.norm.weight, cfg.norm_eps, cfg.norm_weight_offset, groups=cfg.norm_groups)
         return x
 
 

@@ -62,10 +62,12 @@ def _padded_counts(counts: torch.Tensor) -> torch.Tensor:
 
 
 def moe_forward_gather(x: torch.Tensor, topk_w: torch.Tensor, topk_idx: torch.Tensor, experts,
-                       num_experts: int) -> torch.Tensor:
+                       num_experts: int, extra: Optional[torch.Tensor] = None,
+                       extra_gate: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Serving form without expert parallelism: x [T, H]; topk_w [T, k] fp32; topk_idx [T, k] -> fp32 [T, H].  Token rows
     are sorted by expert (no padding: the forward grouped GEMM walks a device-side tile list), and the combine GATHERS
-    every token's k expert rows and sums them in fp32 in the order of its choices - no atomics, no host sync."""
+    every token's k expert rows and sums them in fp32 in the order of its choices - no atomics, no host sync.  `extra`
+    [T, H] (a shared expert's output) joins the sum, times sigmoid(extra_gate [T]) when that is given."""
     from ..ops.moe import gather_combine
 
     T, H = x.shape
@@ -77,7 +79,7 @@ def moe_forward_gather(x: torch.Tensor, topk_w: torch.Tensor, topk_idx: torch.Te
     ys = experts(x.index_select(0, order // k), counts)                # [T*k, H] grouped by expert
     inv = torch.empty_like(order)
     inv[order] = torch.arange(T * k, device=x.device)
-    return gather_combine(ys, inv.view(T, k), topk_w)
+    return gather_combine(ys, inv.view(T, k), topk_w, extra=extra, extra_gate=extra_gate)
 
 
 def moe_forward(x: torch.Tensor, topk_w: torch.Tensor, topk_idx: torch.Tensor, experts, num_experts: int,

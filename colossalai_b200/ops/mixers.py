@@ -27,7 +27,8 @@ from ._dtypes import code
 __all__ = ["RaggedMeta", "short_conv_silu", "state_scan_decay", "state_scan_delta", "gated_group_rms_norm",
            "rms_norm_residual", "rms_norm_f32in", "paged_kv_write_mix", "paged_bias_attention", "log_bucket_starts",
            "bucket_lut", "rotary_table", "rotary_half", "stream_add_norm", "latent_kv_write", "state_scan_ssd",
-           "state_scan_mlstm", "lru_scan", "rotary_unit_norm", "sigmoid_gate_mul", "norm_mean"]
+           "state_scan_mlstm", "lru_scan", "rotary_unit_norm", "sigmoid_gate_mul", "norm_mean", "depth_mix", "poly_norm",
+           "head_rms_norm", "distance_slopes"]
 
 _lib = None
 _SPLIT_BELOW_TILES = 148        # attention steps with fewer CTAs than SMs split their keys
@@ -157,19 +158,42 @@ def bucket_lut(starts: Sequence[int]) -> torch.Tensor:
 _rotary_tables = {}
 
 
-def rotary_table(min_len: int, dims: int, base: float, device) -> torch.Tensor:
-    """fp32 [positions, dims]: row p holds cos(p f_i) for i < dims / 2, then sin(p f_i), with f_i = base^(-2 i / dims).
-    Angles are formed in float64 and rounded once.  The table is cached per (dims, base, device) and grows in powers of
-    two, so that positions far beyond any configured length stay exact."""
-    key = (int(dims), float(base), str(device))
+def rotary_frequencies(dims: int, base: float, scaling: Optional[Sequence[float]] = None):
+    """(f [dims / 2] float64, factor on cos / sin).  f_i = base^(-2 i / dims).  `scaling` = (s, n, fast, slow) stretches
+    the slow frequencies for contexts beyond the n positions the model was trained on: with
+    d(t) = dims ln(n / (2 pi t)) / (2 ln base) - the channel that turns t times over n positions - lo = max(floor(d(fast)), 0),
+    hi = min(ceil(d(slow)), dims - 1) and r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), the frequency becomes
+    f_i / s * r_i + f_i * (1 - r_i), and cos and sin are multiplied by 0.1 ln(s) + 1."""
+    f = torch.tensor(float(base), dtype=torch.float64) ** (-torch.arange(0, dims, 2, dtype=torch.float64) / dims)
+    if not scaling:
+        return f, 1.0
+    s, n, fast, slow = [float(v) for v in scaling]
+    d = lambda t: dims * math.log(n / (2.0 * math.pi * t)) / (2.0 * math.log(base))
+    lo = max(math.floor(d(fast)), 0)
+    hi = min(math.ceil(d(slow)), dims - 1)
+    r = ((torch.arange(dims // 2, dtype=torch.float64) - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+    return f / s * r + f * (1.0 - r), 0.1 * math.log(s) + 1.0
+
+
+def rotary_table(min_len: int, dims: int, base: float, device, scaling: Optional[Sequence[float]] = None) -> torch.Tensor:
+    """fp32 [positions, dims]: row p holds c cos(p f_i) for i < dims / 2, then c sin(p f_i), with (f, c) =
+    `rotary_frequencies(dims, base, scaling)`.  Angles are formed in float64 and rounded once.  The table is cached per
+    (dims, base, scaling, device) and grows in powers of two, so that positions far beyond any configured length stay
+    exact."""
+    key = (int(dims), float(base), tuple(float(v) for v in scaling) if scaling else None, str(device))
     tab = _rotary_tables.get(key)
     if tab is None or tab.shape[0] < min_len:
         n = max(1024, 1 << max(int(min_len) - 1, 1).bit_length())
-        f = torch.tensor(float(base), dtype=torch.float64) ** (-torch.arange(0, dims, 2, dtype=torch.float64) / dims)
+        f, c = rotary_frequencies(dims, base, scaling)
         ang = torch.arange(n, dtype=torch.float64)[:, None] * f[None, :]
-        tab = torch.cat([ang.cos(), ang.sin()], 1).float().to(device)
+        tab = (torch.cat([ang.cos(), ang.sin()], 1) * c).float().to(device)
         _rotary_tables[key] = tab
     return tab
+
+
+def distance_slopes(heads: int) -> torch.Tensor:
+    """fp32 [heads]: 2^(-8 (h + 1) / heads), the per-head slope of a linear distance penalty."""
+    return torch.tensor([2.0 ** (-8.0 * (h + 1) / heads) for h in range(heads)], dtype=torch.float64).float()
 
 
 def _rot_ref(x: torch.Tensor, pos: torch.Tensor, table: torch.Tensor, dims: int) -> torch.Tensor:
@@ -306,18 +330,20 @@ def state_scan_decay(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, head_dec
 def state_scan_delta(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay_pre: torch.Tensor, beta_pre: torch.Tensor,
                      a_log: torch.Tensor, dt_bias: torch.Tensor, state: torch.Tensor, meta: RaggedMeta, heads: int,
                      qk_heads: int, dim: int, vdim: int, unit_eps: float = 1e-6,
-                     q_scale: Optional[float] = None) -> torch.Tensor:
+                     q_scale: Optional[float] = None, head_decay: bool = False) -> torch.Tensor:
     """Gated delta rule with one decay per head and key channel.  Per token and head: q, k -> unit vectors (q also times
     `q_scale`), row decays r = exp(-exp(a_log_h) * softplus(decay_pre + dt_bias)), write strength w = sigmoid(beta_pre);
     the head's matrix M [dim, vdim] is first decayed row by row (M <- diag(r) M), then corrected towards v along k
     (e = w * (v - M^T k); M <- M + outer(k, e)) and read after the write (y = M^T q).  q, k [T, qk_heads x dim] (head h reads
-    h // (heads / qk_heads)), v [T, heads x vdim], decay_pre [T, heads x dim], beta_pre [T, heads]; fp32 state."""
+    h // (heads / qk_heads)), v [T, heads x vdim], decay_pre [T, heads x dim], beta_pre [T, heads]; fp32 state.
+    With `head_decay` the decay is ONE number per head and token: decay_pre [T, heads], dt_bias [heads]."""
     if dim > 256:
         raise NotImplementedError("state_scan: key width above 256 is not supported")
     q_scale = dim ** -0.5 if q_scale is None else q_scale
     if use_native(q):
+        assert decay_pre.stride(1) == 1 and beta_pre.stride(1) == 1
         return _scan_native(1, q, k, v, decay_pre, beta_pre, None, a_log, dt_bias, state, meta, heads, qk_heads, dim,
-                            vdim, False, True, unit_eps, q_scale)
+                            vdim, False, True, unit_eps, q_scale, gate_kind=3 if head_decay else 0)
     T = q.shape[0]
     out = torch.empty(T, heads * vdim, dtype=torch.float32)
     rep = heads // qk_heads
@@ -333,8 +359,9 @@ def state_scan_delta(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay_pr
         kk = kk / torch.sqrt((kk * kk).sum(-1, keepdim=True) + unit_eps)
         qq, kk = qq.repeat_interleave(rep, 1), kk.repeat_interleave(rep, 1)
         vv = v[t0:t0 + n].float().view(n, heads, vdim)
-        g = torch.exp(-A * F.softplus(decay_pre[t0:t0 + n].float().view(n, heads, dim)
-                                      + dt_bias.float().view(1, heads, dim)))
+        gd = 1 if head_decay else dim
+        g = torch.exp(-A * _softplus(decay_pre[t0:t0 + n].float().view(n, heads, gd)
+                                     + dt_bias.float().view(1, heads, gd)))
         beta = torch.sigmoid(beta_pre[t0:t0 + n].float())
         for t in range(n):
             S = g[t][:, :, None] * S
@@ -510,36 +537,108 @@ def gated_group_rms_norm(o: torch.Tensor, weight: Optional[torch.Tensor], gate: 
     return y.to(out_dtype)
 
 
+def _group_rms(y: torch.Tensor, groups: int, eps: float) -> torch.Tensor:
+    T, W = y.shape
+    g = y.view(T, groups, W // groups)
+    return (g / torch.sqrt((g * g).mean(-1, keepdim=True) + eps)).reshape(T, W)
+
+
 def rms_norm_residual(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float, mult: float = 1.0,
-                      offset: float = 0.0, want_cast: bool = True) -> Optional[torch.Tensor]:
-    """x [T, W] fp32, updated in place: x += mult * y / rms(y) * (offset + weight).  Returns x in y's dtype."""
+                      offset: float = 0.0, want_cast: bool = True, groups: int = 1) -> Optional[torch.Tensor]:
+    """x [T, W] fp32, updated in place: x += mult * y / rms(y) * (offset + weight); with `groups` > 1 the row of y is cut
+    into that many equal consecutive parts and each is divided by its own root mean square.  y is in the weight's dtype
+    or fp32 (a sum kept in fp32).  Returns x in the weight's dtype."""
     T, W = x.shape
-    assert x.dtype == torch.float32
+    assert x.dtype == torch.float32 and W % groups == 0
     if use_native(x):
-        assert x.is_contiguous() and y.stride(1) == 1 and weight.dtype == y.dtype
-        h = torch.empty(T, W, dtype=y.dtype, device=x.device) if want_cast else None
-        loader.check(_get_lib().cb_rmsnorm_residual(loader.ptr(x), loader.ptr(y), _i64(y.stride(0)), loader.ptr(weight),
-                                                    loader.ptr(h), _i64(T), W, _f(eps), _f(mult), _f(offset),
-                                                    code(y.dtype), loader.stream_ptr()), "rmsnorm_residual")
+        assert x.is_contiguous() and y.stride(1) == 1 and y.dtype in (weight.dtype, torch.float32)
+        h = torch.empty(T, W, dtype=weight.dtype, device=x.device) if want_cast else None
+        loader.check(_get_lib().cb_rmsnorm_residual(
+            loader.ptr(x), loader.ptr(y), _i64(y.stride(0)), int(y.dtype == torch.float32 and weight.dtype != torch.float32),
+            loader.ptr(weight), loader.ptr(h), _i64(T), W, int(groups), _f(eps), _f(mult), _f(offset), code(weight.dtype),
+            loader.stream_ptr()), "rmsnorm_residual")
         loader.launch_counter.add("rmsnorm_residual")
         return h
-    yf = y.float()
-    x += mult * (yf / torch.sqrt((yf * yf).mean(-1, keepdim=True) + eps) * (offset + weight.float()))
-    return x.to(y.dtype) if want_cast else None
+    x += mult * (_group_rms(y.float(), groups, eps) * (offset + weight.float()))
+    return x.to(weight.dtype) if want_cast else None
 
 
-def rms_norm_f32in(x: torch.Tensor, weight: torch.Tensor, eps: float, offset: float = 0.0) -> torch.Tensor:
-    """x [T, W] fp32 -> x / rms(x) * (offset + weight) in the weight's dtype."""
+def rms_norm_f32in(x: torch.Tensor, weight: torch.Tensor, eps: float, offset: float = 0.0, groups: int = 1) -> torch.Tensor:
+    """x [T, W] fp32 (unit stride inside a row) -> x / rms(x) * (offset + weight) in the weight's dtype; with `groups` > 1
+    every one of that many equal consecutive parts of the row is divided by its own root mean square."""
     T, W = x.shape
+    assert W % groups == 0
     if use_native(x):
+        assert x.stride(1) == 1 and x.dtype == torch.float32
         out = torch.empty(T, W, dtype=weight.dtype, device=x.device)
-        loader.check(_get_lib().cb_rmsnorm_f32in(loader.ptr(x.contiguous()), loader.ptr(weight), loader.ptr(out), _i64(T), W,
-                                                 _f(eps), _f(offset), code(weight.dtype), loader.stream_ptr()),
-                     "rmsnorm_f32in")
+        loader.check(_get_lib().cb_rmsnorm_f32in(loader.ptr(x), _i64(x.stride(0)), loader.ptr(weight), loader.ptr(out),
+                                                 _i64(T), W, int(groups), _f(eps), _f(offset), code(weight.dtype),
+                                                 loader.stream_ptr()), "rmsnorm_f32in")
         loader.launch_counter.add("rmsnorm_f32in")
         return out
-    xf = x.float()
-    return (xf / torch.sqrt((xf * xf).mean(-1, keepdim=True) + eps) * (offset + weight.float())).to(weight.dtype)
+    return (_group_rms(x.float(), groups, eps) * (offset + weight.float())).to(weight.dtype)
+
+
+def depth_mix(hist: torch.Tensor, n: int, coef: torch.Tensor, out: torch.Tensor,
+              cast_dtype: Optional[torch.dtype] = None) -> Optional[torch.Tensor]:
+    """Weighted sum over the history of an fp32 residual stream: out = sum_{j < n} coef[j] * hist[j], j ascending, in fp32.
+    hist [slices, T, W] fp32 (contiguous), coef [>= n] fp32 on the device, out [T, W] fp32 (may be a later slice of
+    `hist`).  With `cast_dtype` the sum is also returned in that dtype (what the next layer's GEMMs read)."""
+    T, W = out.shape
+    assert hist.dtype == torch.float32 and out.dtype == torch.float32 and coef.dtype == torch.float32 and n <= hist.shape[0]
+    want = cast_dtype is not None and cast_dtype != torch.float32
+    if use_native(hist) and (T * W) % 4 == 0:
+        assert hist.is_contiguous() and out.is_contiguous() and coef.is_contiguous()
+        h = torch.empty(T, W, dtype=cast_dtype, device=out.device) if want else None
+        loader.check(_get_lib().cb_depth_mix(loader.ptr(hist), _i64(hist.stride(0)), int(n), loader.ptr(coef),
+                                             loader.ptr(out), loader.ptr(h), _i64(T * W),
+                                             code(cast_dtype if want else torch.float32), loader.stream_ptr()), "depth_mix")
+        loader.launch_counter.add("depth_mix")
+        return h if want else (out if cast_dtype is not None else None)
+    acc = coef[0] * hist[0]
+    for j in range(1, n):
+        acc = acc + coef[j] * hist[j]
+    out.copy_(acc)
+    return None if cast_dtype is None else out.to(cast_dtype)
+
+
+def poly_norm(z: torch.Tensor, coef: torch.Tensor, eps: float) -> torch.Tensor:
+    """z [T, F] -> a N(z) + b N(z^2) + c N(z^3) + e, powers element by element, N(u) = u / sqrt(mean(u^2) + eps) over the
+    row; coef = (a, b, c, e) fp32 on the device.  fp32 arithmetic, result in z's dtype."""
+    T, Fw = z.shape
+    if use_native(z):
+        assert z.stride(1) == 1 and coef.dtype == torch.float32 and coef.numel() == 4 and coef.is_contiguous()
+        out = torch.empty(T, Fw, dtype=z.dtype, device=z.device)
+        loader.check(_get_lib().cb_poly_norm(loader.ptr(z), _i64(z.stride(0)), loader.ptr(out), _i64(T), Fw, loader.ptr(coef),
+                                             _f(eps), code(z.dtype), loader.stream_ptr()), "poly_norm")
+        loader.launch_counter.add("poly_norm")
+        return out
+    zf = z.float()
+    c = coef.float()
+    n = lambda u: u / torch.sqrt((u * u).mean(-1, keepdim=True) + eps)
+    return (c[0] * n(zf) + c[1] * n(zf * zf) + c[2] * n(zf * zf * zf) + c[3]).to(z.dtype)
+
+
+def head_rms_norm(x: torch.Tensor, heads_a: int, heads_b: int, dim: int, weight_a: torch.Tensor,
+                  weight_b: Optional[torch.Tensor], eps: float) -> torch.Tensor:
+    """x [T, >= (heads_a + heads_b) x dim] (unit stride inside a row): every head is divided by its root mean square over
+    its `dim` channels and multiplied by a weight [dim] that the heads share - `weight_a` for the first `heads_a` heads
+    (queries), `weight_b` for the next `heads_b` (keys).  Returns a new [T, (heads_a + heads_b) x dim] tensor."""
+    T = x.shape[0]
+    H = heads_a + heads_b
+    if use_native(x):
+        assert x.stride(1) == 1 and weight_a.dtype == x.dtype and (weight_b is None or weight_b.dtype == x.dtype)
+        out = torch.empty(T, H * dim, dtype=x.dtype, device=x.device)
+        loader.check(_get_lib().cb_head_rmsnorm(loader.ptr(x), _i64(x.stride(0)), loader.ptr(out), _i64(out.stride(0)),
+                                                _i64(T), H, heads_a, dim, loader.ptr(weight_a), loader.ptr(weight_b), _f(eps),
+                                                code(x.dtype), loader.stream_ptr()), "head_rmsnorm")
+        loader.launch_counter.add("head_rmsnorm")
+        return out
+    y = x[:, : H * dim].float().reshape(T, H, dim)
+    y = y / torch.sqrt((y * y).mean(-1, keepdim=True) + eps)
+    w = torch.cat([weight_a.float()[None].expand(heads_a, dim)] +
+                  ([weight_b.float()[None].expand(heads_b, dim)] if heads_b else []), 0)
+    return (y * w[None]).reshape(T, H * dim).to(x.dtype)
 
 
 def norm_mean(parts: Sequence[torch.Tensor], weights: Sequence[torch.Tensor], eps: float) -> torch.Tensor:
@@ -723,7 +822,9 @@ def paged_bias_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
                          meta: RaggedMeta, scale: float, bias_table: Optional[torch.Tensor] = None,
                          bucket_starts: Optional[torch.Tensor] = None, sink: bool = False,
                          lut: Optional[torch.Tensor] = None, tensor_cores: Optional[bool] = None,
-                         vdim: Optional[int] = None, mask_block: int = 0, wide_weights: bool = False) -> torch.Tensor:
+                         vdim: Optional[int] = None, mask_block: int = 0, wide_weights: bool = False,
+                         sink_values: Optional[torch.Tensor] = None, slopes: Optional[torch.Tensor] = None,
+                         window: int = 0) -> torch.Tensor:
     """Causal attention of every step token over positions 0..pos of its sequence in the paged cache; with `mask_block`
     only over the positions of its own block, floor(pos / mask_block) * mask_block .. pos (blocks are counted from the
     start of the sequence, whatever the step's cut).
@@ -731,7 +832,9 @@ def paged_bias_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
     attention: one row per token serves as key and value).
     q [T, heads x dim]; caches [blocks, block_size, kv_heads, dim | vdim]; bias_table [buckets, heads] fp32 indexed by
     the bucket of the distance (`bucket_starts` [buckets] int32: smallest distance of each bucket); `sink` adds a key of
-    score 0 without a value to the softmax.  Returns [T, heads x vdim].
+    score 0 without a value to the softmax - with `sink_values` [heads] fp32 a key of that (unscaled) score per head.
+    `slopes` [heads] fp32 takes slope * (pos - key position) off every score; `window` > 0 keeps only the keys
+    pos - window + 1 .. pos.  Returns [T, heads x vdim].
 
     Two kernels: 16-bit inputs whose head widths are multiples of 8 up to 256 run on tensor cores (`lut` = `bucket_lut`
     of the same buckets; built here when absent); everything else - fp32 above all - takes the exact CUDA-core kernel.
@@ -765,6 +868,8 @@ def paged_bias_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
             max_len = max(c + n for c, n in zip(meta.ctx_lens, meta.q_lens))
             if mask_block:
                 max_len = min(max_len, mask_block + 64)       # keys a tile can see: the split is sized for those
+            if window:
+                max_len = min(max_len, window + 64)
             chunk = splits = 0
             part_o = part_ml = None
             if tiles < _SPLIT_BELOW_TILES and max_len >= 256:
@@ -775,7 +880,7 @@ def paged_bias_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
                     part_ml = _workspace("attn_ml", T * heads * splits * 2, q.device)
                 else:
                     chunk = splits = 0
-            if mask_block and splits:
+            if (mask_block or window) and splits:
                 max_len = max(c + n for c, n in zip(meta.ctx_lens, meta.q_lens))
                 splits = -(-max_len // chunk)                 # chunks are counted from key 0
                 part_o = _workspace("attn_o", T * heads * splits * vdim, q.device)
@@ -785,8 +890,8 @@ def paged_bias_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
                 loader.ptr(meta.cu_q), loader.ptr(meta.ctx_len), loader.ptr(meta.token_pos), loader.ptr(bias_table),
                 loader.ptr(lut), 0 if lut is None else lut.numel(), nb, loader.ptr(out), _i64(T), meta.nseq, meta.max_q,
                 heads, G, dim, vdim, ldv, bs, block_tables.shape[1], _f(scale), int(sink), chunk, splits,
-                loader.ptr(part_o), loader.ptr(part_ml), int(mask_block), int(wide_weights), code(q.dtype),
-                loader.stream_ptr()),
+                loader.ptr(part_o), loader.ptr(part_ml), int(mask_block), int(wide_weights), loader.ptr(sink_values),
+                loader.ptr(slopes), int(window), code(q.dtype), loader.stream_ptr()),
                 "paged_bias_attention_mma")
             loader.launch_counter.add("paged_bias_attention_mma")
             return out
@@ -794,7 +899,8 @@ def paged_bias_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
             loader.ptr(q), _i64(q.stride(0)), loader.ptr(k_cache), loader.ptr(v_cache), loader.ptr(block_tables),
             loader.ptr(meta.token_seq), loader.ptr(meta.token_pos), loader.ptr(bias_table), loader.ptr(bucket_starts), nb,
             loader.ptr(out), _i64(T), heads, G, dim, vdim, ldv, bs, block_tables.shape[1], _f(scale), int(sink),
-            int(mask_block), code(q.dtype), loader.stream_ptr()), "paged_bias_attention")
+            int(mask_block), loader.ptr(sink_values), loader.ptr(slopes), int(window), code(q.dtype),
+            loader.stream_ptr()), "paged_bias_attention")
         loader.launch_counter.add("paged_bias_attention")
         return out
     out = torch.empty(T, heads * vdim, dtype=q.dtype)
@@ -817,8 +923,13 @@ def paged_bias_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
         if mask_block:
             same = (torch.arange(c, L)[:, None] // mask_block) == (torch.arange(L)[None, :] // mask_block)
             s = s.masked_fill(~same[None], float("-inf"))
+        if window:
+            s = s.masked_fill(dist[None] >= window, float("-inf"))
+        if slopes is not None:
+            s = s - slopes.float()[:, None, None] * dist.clamp(min=0)[None].float()
         if sink:
-            s = torch.cat([s, torch.zeros(heads, n, 1)], -1)
+            sv = torch.zeros(heads) if sink_values is None else sink_values.float()
+            s = torch.cat([s, sv[:, None, None].expand(heads, n, 1)], -1)
         p = torch.softmax(s, -1)[..., :L]
         out[t0:t0 + n] = torch.einsum("hij,jhv->ihv", p, vv).reshape(n, heads * vdim).to(q.dtype)
         t0 += n

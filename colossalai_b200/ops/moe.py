@@ -6,6 +6,7 @@
 """
 from __future__ import annotations
 
+import ctypes
 from typing import Optional, Tuple
 
 import torch
@@ -152,19 +153,30 @@ def router_topk(logits: torch.Tensor, k: int, renormalize: bool = True, return_p
     return (w, idx, probs) if return_probs else (w, idx)
 
 
-def gather_combine(rows: torch.Tensor, row_of: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
+def gather_combine(rows: torch.Tensor, row_of: torch.Tensor, weights: torch.Tensor,
+                   extra: Optional[torch.Tensor] = None, extra_gate: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out[t] = sum_j weights[t, j] * rows[row_of[t, j]] in fp32, j ascending.  rows [N, H] (any float dtype), row_of
-    [T, k] int64, weights [T, k] fp32 -> fp32 [T, H]."""
+    [T, k] int64, weights [T, k] fp32 -> fp32 [T, H].  `extra` [T, H] (rows' dtype) is a row that every token takes on
+    top (a shared expert's output), multiplied by sigmoid(extra_gate[t]) when `extra_gate` [T] or [T, 1] fp32 is given."""
     T, k = row_of.shape
     H = rows.shape[1]
     if use_native(rows):
         out = torch.empty(T, H, dtype=torch.float32, device=rows.device)
-        loader.check(_get_lib().cb_moe_gather_combine(loader.ptr(rows.contiguous()), loader.ptr(row_of.contiguous()),
-                                                      loader.ptr(weights.float().contiguous()), loader.ptr(out), T, k, H,
-                                                      code(rows.dtype), loader.stream_ptr()), "moe_gather_combine")
+        if extra is not None:
+            assert extra.stride(1) == 1 and extra.dtype == rows.dtype and extra.shape == (T, H)
+        if extra_gate is not None:
+            assert extra is not None and extra_gate.dtype == torch.float32 and extra_gate.numel() == T
+        loader.check(_get_lib().cb_moe_gather_combine(
+            loader.ptr(rows.contiguous()), loader.ptr(row_of.contiguous()), loader.ptr(weights.float().contiguous()),
+            loader.ptr(out), T, k, H, loader.ptr(extra), ctypes.c_int64(0 if extra is None else extra.stride(0)),
+            loader.ptr(extra_gate), ctypes.c_int64(0 if extra_gate is None else extra_gate.stride(0)),
+            code(rows.dtype), loader.stream_ptr()), "moe_gather_combine")
         loader.launch_counter.add("moe_gather_combine")
         return out
     out = torch.zeros(T, H, dtype=torch.float32, device=rows.device)
     for j in range(k):
         out = out + weights[:, j:j + 1].float() * rows.index_select(0, row_of[:, j]).float()
+    if extra is not None:
+        g = 1.0 if extra_gate is None else torch.sigmoid(extra_gate.float().reshape(T, 1))
+        out = out + g * extra.float()
     return out
