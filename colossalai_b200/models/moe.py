@@ -232,7 +232,10 @@ class ClampedExpertFF(nn.Module):
             return ops.glu(h, "silu", valid_rows=valid_rows if h.is_cuda else None)
         return ops.clamped_glu(h, self.spec.limit, self.spec.alpha, valid_rows=valid_rows if h.is_cuda else None)
 
-    def route(self, x: torch.Tensor):
+    def route(self, x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        return self.route_and_gate(x)[:2]
+
+    def route_and_gate(self, x: torch.Tensor):
         """(weights fp32 [T, top], experts [T, top], the shared expert's gate logit fp32 [T] or None)."""
         from ..ops.moe import router_topk
 
@@ -254,7 +257,7 @@ class ClampedExpertFF(nn.Module):
         from ..moe import dispatch_combine
 
         x2 = x.reshape(-1, x.shape[-1])
-        w, idx, sg = self.route(x2)
+        w, idx, sg = self.route_and_gate(x2)
         if self.spec.shared_gate:
             return dispatch_combine.moe_forward_gather(x2, w, idx, self.experts, self.spec.experts,
                                                        extra=self.shared(x2), extra_gate=sg)
