@@ -47,7 +47,8 @@ def parse_args():
                    help="train: the headline training step (default, described above).  hybrid-serve: prefill / decode "
                         "throughput of the hybrid decoder beside Llama at equal size and its kernels against their "
                         "rooflines (examples/inference/benchmark_hybrid.py; extra flags are passed on, e.g. "
-                        "`--family palilix` / `--family pogorax`: that family beside the hybrid decoder)")
+                        "`--family palilix` / `--family pogorax` / `--family domorax`: that family beside the hybrid "
+                        "decoder)")
     p.add_argument("--model", default=os.environ.get("CB200_BENCH_MODEL", "llama3-8b"))
     p.add_argument("--seq", type=int, default=4096)
     p.add_argument("--mbs", type=int, default=1, help="sequences per GPU per step (weak scaling)")

@@ -696,10 +696,17 @@ __global__ void __launch_bounds__(256) gated_group_rmsnorm_wide_kernel(const flo
 // `groups` equal consecutive parts and every part is divided by its own root mean square.  y is the 16-bit type T or
 // (TY = float) an fp32 sum.  VEC = 4: 16-byte accesses of the stream, 8-byte ones of 16-bit operands (group width and
 // strides multiples of 4, checked by the launcher).
+//
+// With `hist` the updated x is slice n - 1 of a stream history [n, T x W] (slices `hstride` apart) and the kernel goes on
+// to the weighted sum over the history, mix = sum_j coef[j] hist[j] (j ascending, the new x last), written to `mix_out`
+// in fp32; h is then cast(mix) instead of cast(x): the layer's last sublayer and the depth average in one pass.
 template <typename T, typename TY, int VEC>
 __global__ void __launch_bounds__(256) rmsnorm_residual_kernel(float* __restrict__ x, const TY* __restrict__ y, int64_t ldy,
                                                                const T* __restrict__ w, T* __restrict__ h, int W,
-                                                               int groups, float eps, float mult, float offset) {
+                                                               int groups, float eps, float mult, float offset,
+                                                               const float* __restrict__ hist, int64_t hstride, int n,
+                                                               const float* __restrict__ coef,
+                                                               float* __restrict__ mix_out) {
   struct alignas(sizeof(T) * VEC) Pack { T v[VEC]; };
   struct alignas(sizeof(TY) * VEC) PackY { TY v[VEC]; };
   struct alignas(sizeof(float) * VEC) PackF { float v[VEC]; };
@@ -726,6 +733,24 @@ __global__ void __launch_bounds__(256) rmsnorm_residual_kernel(float* __restrict
       hv.v[e] = from_f32<T>(xv.v[e]);
     }
     *reinterpret_cast<PackF*>(x + t * W + c0 + i) = xv;
+    if (hist != nullptr) {
+      PackF acc;
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) acc.v[e] = 0.f;
+      for (int j = 0; j + 1 < n; ++j) {
+        const float cj = __ldg(coef + j);
+        const PackF hj = *reinterpret_cast<const PackF*>(hist + j * hstride + t * W + c0 + i);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) acc.v[e] = fmaf(cj, hj.v[e], acc.v[e]);
+      }
+      const float cl = __ldg(coef + n - 1);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) {
+        acc.v[e] = fmaf(cl, xv.v[e], acc.v[e]);
+        hv.v[e] = from_f32<T>(acc.v[e]);
+      }
+      *reinterpret_cast<PackF*>(mix_out + t * W + c0 + i) = acc;
+    }
     if (h != nullptr) *reinterpret_cast<Pack*>(h + t * W + c0 + i) = hv;
   }
 }
@@ -2048,7 +2073,8 @@ int cb_gated_group_rmsnorm(const float* o, const void* w, int wn, const void* ga
 }
 
 int cb_rmsnorm_residual(float* x, const void* y, int64_t ldy, int y_f32, const void* w, void* h, int64_t tokens, int W,
-                        int groups, float eps, float mult, float offset, int dtype, cudaStream_t st) {
+                        int groups, float eps, float mult, float offset, const float* hist, int64_t hstride, int n,
+                        const float* coef, float* mix_out, int dtype, cudaStream_t st) {
   if (tokens == 0) return 0;
   if (groups < 1 || W % groups != 0) return (int)cudaErrorInvalidValue;
   const int Wg = W / groups;
@@ -2056,22 +2082,23 @@ int cb_rmsnorm_residual(float* x, const void* y, int64_t ldy, int y_f32, const v
   CB_DISPATCH_FLOAT(dtype, T, {
     const size_t ysz = y_f32 ? sizeof(float) : sizeof(T);
     const bool vec = Wg % 4 == 0 && ldy % 4 == 0 && ((uintptr_t)y % (4 * ysz)) == 0 &&
-                     ((uintptr_t)w % (4 * sizeof(T))) == 0 && ((uintptr_t)h % (4 * sizeof(T))) == 0 && ((uintptr_t)x % 16) == 0;
+                     ((uintptr_t)w % (4 * sizeof(T))) == 0 && ((uintptr_t)h % (4 * sizeof(T))) == 0 && ((uintptr_t)x % 16) == 0 &&
+                     ((uintptr_t)hist % 16) == 0 && ((uintptr_t)mix_out % 16) == 0 && hstride % 4 == 0 && W % 4 == 0;
     const int per = vec ? Wg / 4 : Wg;
     const int threads = per >= 256 ? 256 : (per + 31) / 32 * 32;
     if (y_f32) {
       if (vec)
         rmsnorm_residual_kernel<T, float, 4><<<grid, threads, 0, st>>>(x, (const float*)y, ldy, (const T*)w, (T*)h, W, groups,
-                                                                      eps, mult, offset);
+                                                                      eps, mult, offset, hist, hstride, n, coef, mix_out);
       else
         rmsnorm_residual_kernel<T, float, 1><<<grid, threads, 0, st>>>(x, (const float*)y, ldy, (const T*)w, (T*)h, W, groups,
-                                                                      eps, mult, offset);
+                                                                      eps, mult, offset, hist, hstride, n, coef, mix_out);
     } else if (vec) {
       rmsnorm_residual_kernel<T, T, 4><<<grid, threads, 0, st>>>(x, (const T*)y, ldy, (const T*)w, (T*)h, W, groups, eps,
-                                                                mult, offset);
+                                                                mult, offset, hist, hstride, n, coef, mix_out);
     } else {
       rmsnorm_residual_kernel<T, T, 1><<<grid, threads, 0, st>>>(x, (const T*)y, ldy, (const T*)w, (T*)h, W, groups, eps,
-                                                                mult, offset);
+                                                                mult, offset, hist, hstride, n, coef, mix_out);
     }
   });
   return CB_LAUNCH_CHECK();

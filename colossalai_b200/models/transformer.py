@@ -56,6 +56,8 @@ class SeqMeta:
     pending: Optional[list] = None              # fp32 stream: sublayer outputs not added yet (the next norm's kernel
                                                 # adds them) and a [W] vector added to every token (`pending_row`)
     pending_row: Optional[torch.Tensor] = None
+    history: Optional[tuple] = None             # depth average: (stream history, terms, their weights, where the sum goes,
+                                                # whether its compute-dtype copy is wanted) for the layer's last sublayer
 
 
 def _use_fused_a2a(x: torch.Tensor, sp_group) -> bool:
@@ -469,14 +471,20 @@ class DecoderLayer(nn.Module):
         h = meta.stream_cast if (fp32_stream and meta.stream_cast is not None) else x.to(dt)
         y = self.self_attn(h, meta, rope, kv_cache)
         kw = dict(mult=cfg.residual_mult, offset=cfg.norm_weight_offset, groups=cfg.norm_groups)
-        last_cast = not (cfg.depth_average and fp32_stream)
+        # depth average: the layer's last sublayer also forms the weighted sum over the stream's history (`meta.history`,
+        # set by the backbone) and returns ITS compute-dtype copy; the last layer's copy is not needed
+        hist = meta.history if cfg.depth_average else None
+        last_cast = hist is None or hist[4]
+        hist = None if hist is None else hist[:4]
         h = ops.rms_norm_residual(x, y, self.input_layernorm.weight, cfg.norm_eps,
-                                  want_cast=self.mlp is not None or last_cast, **kw)
+                                  want_cast=self.mlp is not None or last_cast,
+                                  history=None if self.mlp is not None else hist, **kw)
         if self.mlp is not None:
             y = self.mlp(h)
             if isinstance(y, tuple):
                 y = y[0] if y[1] is None else y[0] + y[1].float()
-            h = ops.rms_norm_residual(x, y, self.post_attention_layernorm.weight, cfg.norm_eps, want_cast=last_cast, **kw)
+            h = ops.rms_norm_residual(x, y, self.post_attention_layernorm.weight, cfg.norm_eps, want_cast=last_cast,
+                                      history=hist, **kw)
         if fp32_stream:
             meta.stream_cast = h
             return x
@@ -711,8 +719,10 @@ class TransformerModel(nn.Module):
         """Layers on an fp32 stream whose results are all kept: with X_0 the embedding output and X_(i+1) the result of
         layer i, layer i + 1 reads sum_(j <= i+1) a_i[j] X_j (a_i = layer i's `depth_weight`), and the final norm reads
         the last such sum.  The history lives in one buffer [layers + 2, T, W]: slice i + 1 first holds layer i's input
-        and becomes its result (the layer updates the stream in place); the mixing kernel writes the next slice and the
+        and becomes its result (the layer updates the stream in place); the kernel of the layer's last sublayer (norm of
+        the sublayer's output + scaled add) also forms the weighted sum, writes it to the next slice and makes the
         compute-dtype copy the next layer's GEMMs read."""
+        assert x.dtype == torch.float32, "the depth average keeps the stream's history in fp32 (`fp32_residual`)"
         cfg = self.cfg
         n = len(self.layers)
         T, W = x.shape
@@ -722,13 +732,12 @@ class TransformerModel(nn.Module):
         hist[1].copy_(x)
         meta.stream_cast = None
         for i, layer in enumerate(self.layers):
-            layer(hist[i + 1], meta, rope, kv_cache)
-            meta.stream_cast = ops.mixers.depth_mix(hist, i + 2, layer.depth_coef(x.device), hist[i + 2],
-                                                    cast_dtype=dt if i + 1 < n else None)
+            meta.history = (hist, i + 2, layer.depth_coef(x.device), hist[i + 2], i + 1 < n)
+            layer(hist[i + 1], meta, rope, kv_cache)         # leaves the next layer's compute-dtype input in stream_cast
             if self.stream_trace is not None:
                 self.stream_trace.append(hist[i + 2].detach().clone())
         x = hist[n + 1]
-        meta.stream_cast = None
+        meta.stream_cast = meta.history = None
         if cfg.final_norm:
             return ops.rms_norm_f32in(x, self.norm.weight, cfg.norm_eps, cfg.norm_weight_offset, groups=cfg.norm_groups)
         return x

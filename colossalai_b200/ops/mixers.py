@@ -544,22 +544,34 @@ def _group_rms(y: torch.Tensor, groups: int, eps: float) -> torch.Tensor:
 
 
 def rms_norm_residual(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float, mult: float = 1.0,
-                      offset: float = 0.0, want_cast: bool = True, groups: int = 1) -> Optional[torch.Tensor]:
+                      offset: float = 0.0, want_cast: bool = True, groups: int = 1,
+                      history: Optional[tuple] = None) -> Optional[torch.Tensor]:
     """x [T, W] fp32, updated in place: x += mult * y / rms(y) * (offset + weight); with `groups` > 1 the row of y is cut
     into that many equal consecutive parts and each is divided by its own root mean square.  y is in the weight's dtype
-    or fp32 (a sum kept in fp32).  Returns x in the weight's dtype."""
+    or fp32 (a sum kept in fp32).  Returns x in the weight's dtype.
+
+    `history` = (hist [slices, T, W] fp32, n, coef [>= n] fp32, out [T, W] fp32) with x = hist[n - 1]: the same pass also
+    forms out = sum_{j < n} coef[j] hist[j] (`depth_mix` with the updated x as the last term), and what is returned is
+    `out` in the weight's dtype instead of x."""
     T, W = x.shape
     assert x.dtype == torch.float32 and W % groups == 0
+    if history is not None:
+        hist, n, coef, mix_out = history
+        assert x.data_ptr() == hist[n - 1].data_ptr() and hist.is_contiguous() and mix_out.is_contiguous()
     if use_native(x):
         assert x.is_contiguous() and y.stride(1) == 1 and y.dtype in (weight.dtype, torch.float32)
         h = torch.empty(T, W, dtype=weight.dtype, device=x.device) if want_cast else None
+        hargs = (None, _i64(0), 0, None, None) if history is None else \
+            (loader.ptr(hist), _i64(hist.stride(0)), int(n), loader.ptr(coef), loader.ptr(mix_out))
         loader.check(_get_lib().cb_rmsnorm_residual(
             loader.ptr(x), loader.ptr(y), _i64(y.stride(0)), int(y.dtype == torch.float32 and weight.dtype != torch.float32),
-            loader.ptr(weight), loader.ptr(h), _i64(T), W, int(groups), _f(eps), _f(mult), _f(offset), code(weight.dtype),
-            loader.stream_ptr()), "rmsnorm_residual")
+            loader.ptr(weight), loader.ptr(h), _i64(T), W, int(groups), _f(eps), _f(mult), _f(offset), *hargs,
+            code(weight.dtype), loader.stream_ptr()), "rmsnorm_residual")
         loader.launch_counter.add("rmsnorm_residual")
         return h
     x += mult * (_group_rms(y.float(), groups, eps) * (offset + weight.float()))
+    if history is not None:
+        return depth_mix(hist, n, coef, mix_out, cast_dtype=weight.dtype if want_cast else None)
     return x.to(weight.dtype) if want_cast else None
 
 

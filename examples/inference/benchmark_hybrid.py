@@ -3,10 +3,12 @@ attention) beside a Llama of equal width, depth and head sizes, both with random
 time of every mixer kernel alone against its roofline.  `--family palilix` runs the Palilix family (parallel layers with
 retention / latent attention, dense and routed feed-forwards, a looped span) beside Gopunex, the closest served family,
 at equal width and number of layer runs, and its kernels beside their like kernels; `--family pogorax` does the same
-for the Pogorax family (pairs of attention and a recurrent mixer side by side, selective state spaces, pre-norm layers).
+for the Pogorax family (pairs of attention and a recurrent mixer side by side, selective state spaces, pre-norm layers),
+`--family domorax` for the Domorax family (windowed latent attention with sinks, convolved attention with distance slopes,
+delta rule with a decay per head, grouped output norms, a depth-weighted stream, normalised-power and routed feed-forwards).
 
     python examples/inference/benchmark_hybrid.py [--sizes 2048x8,4096x4] [--batch 8] [--in_len 2048] [--out_len 64]
-                                                  [--family gopunex|palilix|pogorax]
+                                                  [--family gopunex|palilix|pogorax|domorax]
 
 Also reachable as `python bench.py --workload hybrid-serve`.  One JSON line per (size, family) and one per kernel.
 Timing: CUDA events on the launching stream after warm-up; the kernel timings write a 256 MB buffer between runs (L2
@@ -94,6 +96,30 @@ def pogorax_config(width: int, layers: int, vocab: int = 32000) -> ModelConfig:
                        fp32_residual=True, fp32_logits=True, max_position_embeddings=1 << 20)
 
 
+def domorax_config(width: int, layers: int, vocab: int = 32000, kv_rank: int = 192, rot: int = 64) -> ModelConfig:
+    """Layers [latent attention + dense, convolved attention + routed, delta rule + routed, latent attention + routed, ...].
+    Heads of 128 channels.  Latent attention: queries through a latent of 3/8 of the width, cache rows of kv_rank + rot = 256
+    columns, a window of 1024 positions, learned sinks, frequencies stretched by 4 beyond 4096 positions.  Convolved
+    attention: one key head per four query heads, four taps.  Delta rule: one q / k head per two value heads, four taps.
+    Dense feed-forwards of 4 x width, eight experts of 1 x width (top 2) with a gated shared expert of 2 x width; output
+    norms in 4 groups, residual factor 0.5."""
+    H, d = width // 128, 128
+    lat = MixerSpec(kind="latent", heads=H, kv_heads=1, dim=d - rot, rot_dim=rot, rot_dims=rot, vdim=d, kv_rank=kv_rank,
+                    rot_base=5e5, scale=d ** -0.5, q_rank=width * 3 // 8, window=1024, sink_learned=True,
+                    rot_scaling=[4.0, 4096.0, 32.0, 1.0], wide_weights=True)
+    att = MixerSpec(kind="attention", heads=H, kv_heads=max(H // 4, 1), dim=d, vdim=d, scale=d ** -0.5, conv=4,
+                    head_norm=True, values_from_keys=True, dist_slopes=True, wide_weights=True)
+    dlt = MixerSpec(kind="delta", heads=H, kv_heads=max(H // 2, 1), dim=d, vdim=d, conv=4)
+    moe = ExpertFFSpec(experts=8, top=2, ff=width, act="silu", shared_ff=2 * width, shared_gate=True)
+    order = [(lat, None), (att, moe), (dlt, moe), (lat, moe)]
+    specs = [LayerSpec(mixer=order[i % 4][0], ff=None if order[i % 4][1] else 4 * width, moe=order[i % 4][1],
+                       ff_act=None if order[i % 4][1] else "polynorm") for i in range(layers)]
+    return ModelConfig(model_type="domorax", vocab_size=vocab, hidden_size=width, intermediate_size=4 * width,
+                       layer_specs=specs, norm_eps=1e-5, norm_groups=4, norm_type="rms", hidden_act="polynorm", glu=False,
+                       pos_type="none", norm_placement="sublayer_out", residual_mult=0.5, fp32_residual=True,
+                       depth_average=True, fp32_logits=True, max_position_embeddings=1 << 20)
+
+
 def llama_config(width: int, layers: int, vocab: int = 32000) -> ModelConfig:
     H = width // 128
     # 8/3 x width gated feed-forward = the parameter count of the hybrid's 4 x width plain one
@@ -114,6 +140,10 @@ def build(cfg: ModelConfig):
                 p.normal_(0, 1.0)
             elif n.endswith("v_mix"):
                 p.fill_(0.4)
+            elif n.endswith("act_coef"):
+                p.copy_(torch.tensor([0.6, 0.3, 0.1, 0.0]))
+            elif n.endswith("depth_weight"):
+                p.fill_(1.0 / p.numel())
     return model.eval()
 
 
@@ -488,6 +518,143 @@ def kernels_pogorax(width: int, batch: int, in_len: int) -> list:
     return rows
 
 
+def kernels_domorax(width: int, batch: int, in_len: int, kv_rank: int = 192, rot: int = 64) -> list:
+    """Every kernel of the Domorax layers alone at one layer's sizes beside its like kernel of the closest families."""
+    from colossalai_b200 import ops
+    from colossalai_b200.ops import mixers as M
+    from colossalai_b200.ops import moe as MO
+
+    hbm, tflops, src = peaks()
+    dev, dt = "cuda", torch.bfloat16
+    H, d, bs = width // 128, 128, 64
+    G = max(H // 4, 1)
+    flush = torch.zeros(64 << 20, dtype=torch.float32, device=dev)
+    rows = []
+
+    def rec(name, phase, ms, bytes_, flops, like=""):
+        ideal = max(bytes_ / hbm, flops / tflops) * 1e3
+        rows.append({"kernel": name, "phase": phase + ("(graph replay)" if phase == "decode" else ""), "width": width,
+                     "ms": ms, "roofline_ms": ideal, "frac_of_" + src + "_roofline": ideal / ms,
+                     "bound": "hbm" if bytes_ / hbm > flops / tflops else "tensor", "like": like})
+
+    for phase, q_len, ctx in (("prefill", in_len, 0), ("decode", 1, in_len)):
+        replay = phase == "decode"             # decode kernels are timed as graph replays (no host share)
+        T = batch * q_len
+        L = ctx + q_len
+        meta = M.RaggedMeta.build([q_len] * batch, [ctx] * batch, list(range(batch)), dev)
+        x = lambda c: torch.randn(T, c, device=dev, dtype=dt)
+        # output norm in groups + scaled add, alone and with the depth average over 5 slices  |  like: Gopunex norm + residual
+        n = 5
+        hist = torch.randn(n + 1, T, width, device=dev)
+        coef = torch.full((n,), 1.0 / n, device=dev)
+        y1, w = x(width), torch.ones(width, device=dev, dtype=dt)
+        ms = _time(lambda: M.rms_norm_residual(hist[n - 1], y1, w, 1e-5, 0.5, groups=4), flush, graph=replay)
+        rec("rmsnorm_residual(4 groups)", phase, ms, T * width * (4 + 4 + 2 + 2), 0, like="rmsnorm_residual")
+        ms = _time(lambda: M.rms_norm_residual(hist[n - 1], y1, w, 1e-5, 0.5, groups=4, history=(hist, n, coef, hist[n])),
+                   flush, graph=replay)
+        rec("rmsnorm_residual(4 groups) + depth average(5)", phase, ms, T * width * (2 + 4 + 4 + (n - 1) * 4 + 4 + 2), 0,
+            like="rmsnorm_residual")
+        yf = torch.randn(T, width, device=dev)
+        ms = _time(lambda: M.rms_norm_residual(hist[n - 1], yf, w, 1e-5, 0.5, groups=4), flush, graph=replay)
+        rec("rmsnorm_residual(4 groups, fp32 sum in)", phase, ms, T * width * (4 + 4 + 4 + 2), 0, like="rmsnorm_residual")
+        xs = torch.randn(T, width, device=dev)
+        ms = _time(lambda: M.rms_norm_residual(xs, y1, w, 1e-5, 0.7, 1.0), flush, graph=replay)
+        rec("gopunex:rmsnorm_residual", phase, ms, T * width * (4 + 4 + 2 + 2), 0)
+        # normalised powers  |  like: Llama's gated unit, the other elementwise pass over the feed-forward's hidden vector
+        z, pc = x(4 * width), torch.tensor([0.6, 0.3, 0.1, 0.0], device=dev)
+        ms = _time(lambda: M.poly_norm(z, pc, 1e-5), flush, graph=replay)
+        rec("poly_norm", phase, ms, 2 * T * 4 * width * 2, 0, like="glu_fwd(silu)")
+        gu = x(2 * 4 * width)
+        ms = _time(lambda: ops.glu(gu, "silu"), flush, graph=replay)
+        rec("llama:glu_fwd(silu)", phase, ms, 3 * T * 4 * width * 2, 0)
+        # delta rule with one decay per head  |  like: Gopunex delta rule with a decay per channel
+        Gd = max(H // 2, 1)
+        S = torch.zeros(batch, H, d, d, device=dev)
+        state_bytes = 2 * S.numel() * 4
+        q, k, v, a1, b1 = x(Gd * d) * 0.1, x(Gd * d) * 0.1, x(H * d), x(H), x(H)
+        al, db = torch.zeros(H, device=dev), torch.zeros(H, device=dev)
+        ms = _time(lambda: M.state_scan_delta(q, k, v, a1, b1, al, db, S, meta, H, Gd, d, d, head_decay=True), flush,
+                   graph=replay)
+        rec("state_scan_delta(decay per head)", phase, ms, T * ((2 * Gd + H) * d * 2 + H * d * 4) + state_bytes,
+            6.0 * T * H * d * d, like="state_scan_delta")
+        qg, kg, ag, dbg = x(H * d) * 0.1, x(H * d) * 0.1, x(H * d), torch.zeros(H * d, device=dev)
+        ms = _time(lambda: M.state_scan_delta(qg, kg, v, ag, b1, al, dbg, S, meta, H, H, d, d), flush, graph=replay)
+        rec("gopunex:state_scan_delta", phase, ms, T * (4 * H * d * 2 + H * d * 4) + state_bytes, 6.0 * T * H * d * d)
+        # convolution on q | k without activation, per-head norm  |  like: Gopunex convolution, Llama's in-place rotation
+        Cc = (H + G) * d
+        xc, wc = x(Cc), torch.randn(Cc, 4, device=dev, dtype=dt)
+        stc = torch.zeros(batch, 3, Cc, device=dev, dtype=dt)
+        ms = _time(lambda: M.short_conv_silu(xc, wc, stc, meta, activation=False), flush, graph=replay)
+        rec("short_conv(q | k, no activation)", phase, ms, 2 * T * Cc * 2, 0, like="short_conv_silu")
+        ms = _time(lambda: M.short_conv_silu(xc, wc, stc, meta), flush, graph=replay)
+        rec("gopunex:short_conv_silu", phase, ms, 2 * T * Cc * 2, 0)
+        wh = torch.ones(d, device=dev, dtype=dt)
+        ms = _time(lambda: M.head_rms_norm(xc, H, G, d, wh, wh, 1e-5), flush, graph=replay)
+        rec("head_rms_norm(q | k)", phase, ms, 2 * T * Cc * 2, 0, like="rope_qkv")
+        qkv = x((H + 2 * G) * d)
+        cos, sin = ops.build_rope_cache(L + 1, d, 5e5, device=dev)
+        pos = meta.token_pos.long()
+        ms = _time(lambda: ops.rope_qkv(qkv, pos, cos, sin, H, G, d), flush, graph=replay)
+        rec("llama:rope_qkv", phase, ms, 2 * T * (H + G) * d * 2, 0)
+        o, gate, wn = torch.randn(T, H * d, device=dev), x(H * d), torch.ones(d, device=dev, dtype=dt)
+        ms = _time(lambda: M.gated_group_rms_norm(o, wn, gate, d, 1e-5, dt, gate_act="silu"), flush, graph=replay)
+        rec("gated_group_rmsnorm(silu)", phase, ms, T * H * d * (4 + 2 + 2), 0, like="gated_group_rmsnorm")
+        # query latent norm, cache row of latent attention  |  like: Gopunex K / V page write
+        qr = width * 3 // 8
+        zq, wq = x(qr + kv_rank + rot), torch.ones(qr, device=dev, dtype=dt)
+        ms = _time(lambda: M.head_rms_norm(zq, 1, 0, qr, wq, None, 1e-5), flush, graph=replay)
+        rec("head_rms_norm(query latent)", phase, ms, 2 * T * qr * 2, 0, like="rmsnorm_fwd")
+        per = (L + bs - 1) // bs
+        W2 = kv_rank + rot
+        lc = torch.randn(batch * per, bs, 1, W2, device=dev, dtype=dt)
+        tables = torch.arange(batch * per, dtype=torch.int32, device=dev).view(batch, per)
+        table = M.rotary_table(L + 1, rot, 5e5, dev, [4.0, 4096.0, 32.0, 1.0])
+        wl = torch.ones(kv_rank, device=dev, dtype=dt)
+        ms = _time(lambda: M.latent_kv_write(zq[:, qr:], wl, 1e-5, kv_rank, table, lc, tables, meta), flush, graph=replay)
+        rec("latent_kv_write(stretched frequencies)", phase, ms, 2 * T * W2 * 2, 0, like="paged_kv_write_mix")
+        # attention: latent rows with a window of 1024 and learned sinks; convolved attention with distance slopes (values
+        # in a cache of their own); both with two-term weights  |  like: Palilix latent attention, Gopunex bias + sink
+        win = 1024
+        qa2 = x(H * W2)
+        sinks = torch.randn(H, device=dev)
+        seen = sum(min(p_ + 1, win) for p_ in range(ctx, L)) * batch                  # keys every query sees
+        ms = _time(lambda: M.paged_bias_attention(qa2, lc, lc, tables, meta, d ** -0.5, vdim=kv_rank, window=win, sink=True,
+                                                  sink_values=sinks, wide_weights=True), flush, graph=replay)
+        rec("latent_attention(window 1024, sinks, two-term weights)", phase, ms,
+            batch * min(L, win + q_len) * W2 * 2 + T * H * (W2 + kv_rank) * 2, 2.0 * H * (W2 + kv_rank) * seen,
+            like="latent_attention")
+        full = batch * (q_len * ctx + q_len * (q_len + 1) / 2)
+        ms = _time(lambda: M.paged_bias_attention(qa2, lc, lc, tables, meta, d ** -0.5, vdim=kv_rank), flush, graph=replay)
+        rec("palilix:latent_attention", phase, ms, batch * L * W2 * 2 + T * H * (W2 + kv_rank) * 2,
+            2.0 * H * (W2 + kv_rank) * full)
+        kc = torch.randn(batch * per, bs, G, d, device=dev, dtype=dt)
+        vc = torch.randn(batch * per, bs, G, d, device=dev, dtype=dt)
+        qa = x(H * d)
+        slopes = M.distance_slopes(H).to(dev)
+        kv_bytes = 2 * batch * L * G * d * 2
+        att_flops = 4.0 * H * d * full
+        ms = _time(lambda: M.paged_bias_attention(qa, kc, vc, tables, meta, d ** -0.5, slopes=slopes, wide_weights=True),
+                   flush, graph=replay)
+        rec("paged_attention(distance slopes, two-term weights)", phase, ms, kv_bytes + 2 * T * H * d * 2, att_flops,
+            like="paged_bias_attention")
+        rel = torch.randn(32, H, device=dev)
+        starts_host = M.log_bucket_starts(32, 512.0)
+        starts = torch.tensor(starts_host, dtype=torch.int32, device=dev)
+        lut = M.bucket_lut(starts_host).to(dev)
+        ms = _time(lambda: M.paged_bias_attention(qa, kc, vc, tables, meta, d ** -0.5, rel, starts, True, lut=lut), flush,
+                   graph=replay)
+        rec("gopunex:paged_bias_attention", phase, ms, kv_bytes + 2 * T * H * d * 2, att_flops)
+        # fp32 gather of the chosen experts' rows + the gated shared expert  |  like: Palilix gather
+        ys, sh = x(width).repeat(2, 1), x(width)
+        row_of = torch.randperm(2 * T, device=dev).view(T, 2)
+        wts, sg = torch.rand(T, 2, device=dev), torch.randn(T, 9, device=dev)[:, 8]
+        ms = _time(lambda: MO.gather_combine(ys, row_of, wts, extra=sh, extra_gate=sg), flush, graph=replay)
+        rec("moe_gather_combine(+ gated shared expert)", phase, ms, T * width * (3 * 2 + 4), 0, like="moe_gather_combine")
+        ms = _time(lambda: MO.gather_combine(ys, row_of, wts), flush, graph=replay)
+        rec("palilix:moe_gather_combine", phase, ms, T * width * (2 * 2 + 4), 0)
+    return rows
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--sizes", default="2048x8,4096x4", help="width x layers, comma separated")
@@ -495,9 +662,9 @@ def main(argv=None):
     ap.add_argument("--in_len", type=int, default=2048)
     ap.add_argument("--out_len", type=int, default=32)
     ap.add_argument("--cuda_graph", action="store_true", help="also run both families with CUDA-graph decode steps")
-    ap.add_argument("--family", default="gopunex", choices=["gopunex", "palilix", "pogorax"],
-                    help="gopunex: the hybrid decoder beside Llama (default).  palilix / pogorax: that family beside "
-                         "Gopunex, the closest served family")
+    ap.add_argument("--family", default="gopunex", choices=["gopunex", "palilix", "pogorax", "domorax"],
+                    help="gopunex: the hybrid decoder beside Llama (default).  palilix / pogorax / domorax: that family "
+                         "beside Gopunex, the closest served family")
     ap.add_argument("--no-kernels", action="store_true")
     ap.add_argument("--no-serve", action="store_true")
     args = ap.parse_args(argv)
@@ -508,11 +675,13 @@ def main(argv=None):
             for graph in ([False, True] if args.cuda_graph else [False]):
                 pair = {"gopunex": lambda: (hybrid_config(width, layers), llama_config(width, layers)),
                         "palilix": lambda: (palilix_config(width, layers), hybrid_config(width, layers)),
-                        "pogorax": lambda: (pogorax_config(width, layers), hybrid_config(width, layers))}[args.family]()
+                        "pogorax": lambda: (pogorax_config(width, layers), hybrid_config(width, layers)),
+                        "domorax": lambda: (domorax_config(width, layers), hybrid_config(width, layers))}[args.family]()
                 for cfg in pair:
                     print(json.dumps(serve(cfg, args.batch, args.in_len, args.out_len, graph)), flush=True)
         if not args.no_kernels:
-            kfn = {"gopunex": kernels, "palilix": kernels_palilix, "pogorax": kernels_pogorax}[args.family]
+            kfn = {"gopunex": kernels, "palilix": kernels_palilix, "pogorax": kernels_pogorax,
+                   "domorax": kernels_domorax}[args.family]
             for row in kfn(width, args.batch, args.in_len):
                 print(json.dumps(row), flush=True)
 
