@@ -715,17 +715,33 @@ __global__ void __launch_bounds__(256) rmsnorm_residual_kernel(float* __restrict
   const int Wg = W / groups, c0 = (int)(blockIdx.x % groups) * Wg;
   const TY* yr = y + t * ldy + c0;
   float ss[1] = {0.f};
-  for (int i = threadIdx.x * VEC; i < Wg; i += blockDim.x * VEC) {
-    const PackY a = *reinterpret_cast<const PackY*>(yr + i);
+  // a group that the CTA covers in one step (the usual case): the stream's and the weight's loads are issued together
+  // with y's, ahead of the reduction, so that one round trip to memory serves the whole row
+  const bool one_step = Wg <= (int)blockDim.x * VEC;
+  const int i0 = threadIdx.x * VEC;
+  PackY a0;
+  Pack w0;
+  PackF x0;
+  if (one_step && i0 < Wg) {
+    a0 = *reinterpret_cast<const PackY*>(yr + i0);
+    w0 = *reinterpret_cast<const Pack*>(w + c0 + i0);
+    x0 = *reinterpret_cast<const PackF*>(x + t * W + c0 + i0);
 #pragma unroll
-    for (int e = 0; e < VEC; ++e) ss[0] = fmaf(to_f32<TY>(a.v[e]), to_f32<TY>(a.v[e]), ss[0]);
+    for (int e = 0; e < VEC; ++e) ss[0] = fmaf(to_f32<TY>(a0.v[e]), to_f32<TY>(a0.v[e]), ss[0]);
+  }
+  if (!one_step) {
+    for (int i = threadIdx.x * VEC; i < Wg; i += blockDim.x * VEC) {
+      const PackY a = *reinterpret_cast<const PackY*>(yr + i);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) ss[0] = fmaf(to_f32<TY>(a.v[e]), to_f32<TY>(a.v[e]), ss[0]);
+    }
   }
   block_sum<1>(ss, red);
   const float r = 1.f / sqrtf(ss[0] / (float)Wg + eps);
   for (int i = threadIdx.x * VEC; i < Wg; i += blockDim.x * VEC) {
-    const PackY a = *reinterpret_cast<const PackY*>(yr + i);
-    const Pack ww = *reinterpret_cast<const Pack*>(w + c0 + i);
-    PackF xv = *reinterpret_cast<const PackF*>(x + t * W + c0 + i);
+    const PackY a = one_step ? a0 : *reinterpret_cast<const PackY*>(yr + i);
+    const Pack ww = one_step ? w0 : *reinterpret_cast<const Pack*>(w + c0 + i);
+    PackF xv = one_step ? x0 : *reinterpret_cast<const PackF*>(x + t * W + c0 + i);
     Pack hv;
 #pragma unroll
     for (int e = 0; e < VEC; ++e) {
@@ -797,35 +813,84 @@ __global__ void __launch_bounds__(256) depth_mix_kernel(const float* __restrict_
 
 // Polynomial activation with normalised powers, one CTA per token row: out = a N(z) + b N(z^2) + c N(z^3) + e with powers
 // taken element by element and N(u) = u / sqrt(mean(u^2) + eps) over the row; the three sums of squares (z^2, z^4, z^6)
-// come from one pass, everything in fp32.  coef = (a, b, c, e) on the device.
-template <typename T>
-__global__ void __launch_bounds__(256) poly_norm_kernel(const T* __restrict__ z, int64_t ldz, T* __restrict__ out, int F,
+// come from one pass, everything in fp32.  coef = (a, b, c, e) on the device.  VEC elements per access (16 bytes when the
+// row allows); the first POLY_ITEMS vectors of a thread stay in registers between the two passes, so rows up to
+// threads x POLY_ITEMS x VEC wide (16384 16-bit values with 512 threads) are read once - all their loads in flight
+// together - and wider ones re-read the rest.
+template <typename T, int VEC, int POLY_ITEMS>
+__global__ void __launch_bounds__(512) poly_norm_kernel(const T* __restrict__ z, int64_t ldz, T* __restrict__ out, int F,
                                                         const float* __restrict__ coef, float eps) {
+  struct alignas(sizeof(T) * VEC) Pack { T v[VEC]; };
   __shared__ float red[3 * 32];
   const int64_t t = blockIdx.x;
   const T* zr = z + t * ldz;
+  const int step = blockDim.x * VEC;
+  Pack keep[POLY_ITEMS];
+#pragma unroll
+  for (int it = 0; it < POLY_ITEMS; ++it) {
+    const int i = threadIdx.x * VEC + it * step;
+    if (i < F) keep[it] = *reinterpret_cast<const Pack*>(zr + i);
+  }
   float ss[3] = {0.f, 0.f, 0.f};
-  for (int i = threadIdx.x; i < F; i += blockDim.x) {
-    const float v = to_f32<T>(zr[i]), v2 = v * v;
-    ss[0] += v2;
-    ss[1] = fmaf(v2, v2, ss[1]);
-    ss[2] = fmaf(v2 * v, v2 * v, ss[2]);
+#pragma unroll
+  for (int it = 0; it < POLY_ITEMS; ++it) {
+    if (threadIdx.x * VEC + it * step < F) {
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) {
+        const float v = to_f32<T>(keep[it].v[e]), v2 = v * v;
+        ss[0] += v2;
+        ss[1] = fmaf(v2, v2, ss[1]);
+        ss[2] = fmaf(v2 * v, v2 * v, ss[2]);
+      }
+    }
+  }
+  for (int i = threadIdx.x * VEC + POLY_ITEMS * step; i < F; i += step) {
+    const Pack a = *reinterpret_cast<const Pack*>(zr + i);
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) {
+      const float v = to_f32<T>(a.v[e]), v2 = v * v;
+      ss[0] += v2;
+      ss[1] = fmaf(v2, v2, ss[1]);
+      ss[2] = fmaf(v2 * v, v2 * v, ss[2]);
+    }
   }
   block_sum<3>(ss, red);
   const float r1 = coef[0] / sqrtf(ss[0] / (float)F + eps), r2 = coef[1] / sqrtf(ss[1] / (float)F + eps),
               r3 = coef[2] / sqrtf(ss[2] / (float)F + eps), e0 = coef[3];
-  for (int i = threadIdx.x; i < F; i += blockDim.x) {
-    const float v = to_f32<T>(zr[i]), v2 = v * v;
-    out[t * F + i] = from_f32<T>(fmaf(r1, v, fmaf(r2, v2, fmaf(r3, v2 * v, e0))));
+#pragma unroll
+  for (int it = 0; it < POLY_ITEMS; ++it) {
+    const int i = threadIdx.x * VEC + it * step;
+    if (i < F) {
+      Pack o;
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) {
+        const float v = to_f32<T>(keep[it].v[e]), v2 = v * v;
+        o.v[e] = from_f32<T>(fmaf(r1, v, fmaf(r2, v2, fmaf(r3, v2 * v, e0))));
+      }
+      *reinterpret_cast<Pack*>(out + t * F + i) = o;
+    }
+  }
+  for (int i = threadIdx.x * VEC + POLY_ITEMS * step; i < F; i += step) {
+    const Pack a = *reinterpret_cast<const Pack*>(zr + i);
+    Pack o;
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) {
+      const float v = to_f32<T>(a.v[e]), v2 = v * v;
+      o.v[e] = from_f32<T>(fmaf(r1, v, fmaf(r2, v2, fmaf(r3, v2 * v, e0))));
+    }
+    *reinterpret_cast<Pack*>(out + t * F + i) = o;
   }
 }
 
 // RMS norm of every head of a [T, heads x dim] projection with one weight over the head's channels, shared by the heads:
-// the first `heads_a` heads take `wa`, the others `wb` (query heads, then key heads).  One warp per (token, head), fp32.
-template <typename T>
+// the first `heads_a` heads take `wa`, the others `wb` (query heads, then key heads).  One warp per (token, head), fp32;
+// VEC channels per access, the first HEAD_ITEMS vectors of a lane stay in registers between the two passes (1: heads up
+// to 32 x VEC channels, one load per lane and few registers; 8: wide rows such as a query latent).
+template <typename T, int VEC, int HEAD_ITEMS>
 __global__ void __launch_bounds__(128) head_rmsnorm_kernel(const T* __restrict__ x, int64_t ldx, T* __restrict__ out,
                                                            int64_t ldo, int64_t tokens, int heads, int heads_a, int dim,
                                                            const T* __restrict__ wa, const T* __restrict__ wb, float eps) {
+  struct alignas(sizeof(T) * VEC) Pack { T v[VEC]; };
   const int lane = threadIdx.x & 31;
   const int64_t unit = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (unit >= tokens * heads) return;
@@ -833,10 +898,43 @@ __global__ void __launch_bounds__(128) head_rmsnorm_kernel(const T* __restrict__
   const int hd = (int)(unit % heads);
   const T* row = x + t * ldx + hd * dim;
   const T* w = hd < heads_a ? wa : wb;
+  Pack keep[HEAD_ITEMS];
   float ss = 0.f;
-  for (int i = lane; i < dim; i += 32) { const float v = to_f32<T>(row[i]); ss = fmaf(v, v, ss); }
+#pragma unroll
+  for (int it = 0; it < HEAD_ITEMS; ++it) {
+    const int i = (lane + 32 * it) * VEC;
+    if (i < dim) {
+      keep[it] = *reinterpret_cast<const Pack*>(row + i);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) { const float v = to_f32<T>(keep[it].v[e]); ss = fmaf(v, v, ss); }
+    }
+  }
+  for (int i = (lane + 32 * HEAD_ITEMS) * VEC; i < dim; i += 32 * VEC) {
+    const Pack a = *reinterpret_cast<const Pack*>(row + i);
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) { const float v = to_f32<T>(a.v[e]); ss = fmaf(v, v, ss); }
+  }
   const float r = 1.f / sqrtf(warp_sum(ss) / (float)dim + eps);
-  for (int i = lane; i < dim; i += 32) out[t * ldo + hd * dim + i] = from_f32<T>(to_f32<T>(row[i]) * r * to_f32<T>(w[i]));
+  T* orow = out + t * ldo + hd * dim;
+#pragma unroll
+  for (int it = 0; it < HEAD_ITEMS; ++it) {
+    const int i = (lane + 32 * it) * VEC;
+    if (i < dim) {
+      const Pack ww = *reinterpret_cast<const Pack*>(w + i);
+      Pack o;
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) o.v[e] = from_f32<T>(to_f32<T>(keep[it].v[e]) * r * to_f32<T>(ww.v[e]));
+      *reinterpret_cast<Pack*>(orow + i) = o;
+    }
+  }
+  for (int i = (lane + 32 * HEAD_ITEMS) * VEC; i < dim; i += 32 * VEC) {
+    const Pack a = *reinterpret_cast<const Pack*>(row + i);
+    const Pack ww = *reinterpret_cast<const Pack*>(w + i);
+    Pack o;
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) o.v[e] = from_f32<T>(to_f32<T>(a.v[e]) * r * to_f32<T>(ww.v[e]));
+    *reinterpret_cast<Pack*>(orow + i) = o;
+  }
 }
 
 // ------------------------------------------------------------------------------------------------ stream sums + norm
@@ -2132,7 +2230,21 @@ int cb_poly_norm(const void* z, int64_t ldz, void* out, int64_t tokens, int F, c
                  cudaStream_t st) {
   if (tokens == 0) return 0;
   CB_DISPATCH_FLOAT(dtype, T, {
-    poly_norm_kernel<T><<<(unsigned)tokens, 256, 0, st>>>((const T*)z, ldz, (T*)out, F, coef, eps);
+    constexpr int V = 16 / sizeof(T);
+    const bool vec = F % V == 0 && ldz % V == 0 && ((uintptr_t)z & 15) == 0 && ((uintptr_t)out & 15) == 0;
+    if (vec) {
+      const int nv = F / V;                       // vectors of a row: 2 per thread up to 256 threads, then 4, then 512 threads
+      if (nv <= 512) {
+        const int threads = (nv / 2 + 31) / 32 * 32;
+        poly_norm_kernel<T, V, 2><<<(unsigned)tokens, threads < 32 ? 32 : threads, 0, st>>>((const T*)z, ldz, (T*)out, F,
+                                                                                           coef, eps);
+      } else {
+        poly_norm_kernel<T, V, 4><<<(unsigned)tokens, nv <= 1024 ? 256 : 512, 0, st>>>((const T*)z, ldz, (T*)out, F, coef,
+                                                                                      eps);
+      }
+    } else {
+      poly_norm_kernel<T, 1, 4><<<(unsigned)tokens, 256, 0, st>>>((const T*)z, ldz, (T*)out, F, coef, eps);
+    }
   });
   return CB_LAUNCH_CHECK();
 }
@@ -2142,8 +2254,20 @@ int cb_head_rmsnorm(const void* x, int64_t ldx, void* out, int64_t ldo, int64_t 
   if (tokens == 0 || heads == 0) return 0;
   const int64_t units = tokens * heads;
   CB_DISPATCH_FLOAT(dtype, T, {
-    head_rmsnorm_kernel<T><<<(unsigned)((units + 3) / 4), 128, 0, st>>>((const T*)x, ldx, (T*)out, ldo, tokens, heads,
-                                                                       heads_a, dim, (const T*)wa, (const T*)wb, eps);
+    constexpr int V = 8 / sizeof(T);              // 8-byte accesses: a warp covers a head of 128 16-bit channels at once
+    const size_t al = V * sizeof(T);
+    const bool vec = dim % V == 0 && ldx % V == 0 && ldo % V == 0 && ((uintptr_t)x % al) == 0 && ((uintptr_t)out % al) == 0 &&
+                     ((uintptr_t)wa % al) == 0 && ((uintptr_t)wb % al) == 0;
+    const unsigned grid = (unsigned)((units + 3) / 4);
+    if (vec && dim <= 32 * V)
+      head_rmsnorm_kernel<T, V, 1><<<grid, 128, 0, st>>>((const T*)x, ldx, (T*)out, ldo, tokens, heads, heads_a, dim,
+                                                         (const T*)wa, (const T*)wb, eps);
+    else if (vec)
+      head_rmsnorm_kernel<T, V, 8><<<grid, 128, 0, st>>>((const T*)x, ldx, (T*)out, ldo, tokens, heads, heads_a, dim,
+                                                         (const T*)wa, (const T*)wb, eps);
+    else
+      head_rmsnorm_kernel<T, 1, 4><<<grid, 128, 0, st>>>((const T*)x, ldx, (T*)out, ldo, tokens, heads, heads_a, dim,
+                                                         (const T*)wa, (const T*)wb, eps);
   });
   return CB_LAUNCH_CHECK();
 }

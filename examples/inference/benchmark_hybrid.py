@@ -15,6 +15,7 @@ Timing: CUDA events on the launching stream after warm-up; the kernel timings wr
 flush).  Rooflines use the measured copy bandwidth / bf16 GEMM throughput of MEASURED_PEAKS.json.
 """
 import argparse
+import gc
 import json
 import os
 import sys
@@ -184,7 +185,8 @@ def serve(cfg: ModelConfig, batch: int, in_len: int, out_len: int, cuda_graph: b
            "layer_runs": cfg.num_cache_layers, "batch": batch, "in_len": in_len, "out_len": out_len, "cuda_graph": cuda_graph, "prefill_ms": tp,
            "prefill_tokens_per_s": batch * in_len / (tp / 1e3), "decode_ms_per_step": td / max(steps, 1),
            "decode_tokens_per_s": batch * steps / (td / 1e3), "our_kernel_launches": loader.launch_counter.count}
-    del eng, model
+    del eng, model, run
+    gc.collect()                                # graphs of this engine go now, not in the middle of the next capture
     torch.cuda.empty_cache()
     return out
 
