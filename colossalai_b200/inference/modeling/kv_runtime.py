@@ -113,6 +113,10 @@ class PagedKVRuntime:
         return mops.paged_bias_attention(q, kc, kc, self.block_tables, self.ragged, scale, vdim=kv_rank, window=window,
                                          sink=sink, sink_values=sink_values, wide_weights=wide_weights)
 
+    def pages(self, layer_idx: int):
+        """(key pages, value pages) of the layer's current run, for a mixer whose kernels write the step's rows themselves."""
+        return self.k_caches[self.cache_index(layer_idx)], self.v_caches[self.cache_index(layer_idx)]
+
     def latent_cache(self, layer_idx: int) -> torch.Tensor:
         return self.k_caches[self.cache_index(layer_idx)]
 
@@ -124,11 +128,13 @@ class PagedKVRuntime:
         """Write the step's K / V rows (values optionally blended with `v_other`) into the layer's pages, then attend
         every step token over positions 0..pos of its sequence (with `mask_block`: over the positions of its own block
         of that many positions only; with `window`: over the last `window` positions; `slopes`: a linear distance
-        penalty per head; `sink_values`: the sink's score per head).  q [T, H x dim], k [T, G x dim], v [T, G x vdim]."""
+        penalty per head; `sink_values`: the sink's score per head).  q [T, H x dim], k [T, G x dim], v [T, G x vdim];
+        k = None: the caller has written the step's rows itself (`pages`)."""
         from ...ops import mixers as mops
 
         kc, vc = self.k_caches[self.cache_index(layer_idx)], self.v_caches[self.cache_index(layer_idx)]
-        mops.paged_kv_write_mix(k, v, kc, vc, self.block_tables, self.ragged, v_other=v_other, lam=lam)
+        if k is not None:
+            mops.paged_kv_write_mix(k, v, kc, vc, self.block_tables, self.ragged, v_other=v_other, lam=lam)
         return mops.paged_bias_attention(q, kc, vc, self.block_tables, self.ragged, scale, bias_table=bias_table,
                                          bucket_starts=bucket_starts, sink=sink, lut=lut, mask_block=mask_block,
                                          wide_weights=wide_weights, sink_values=sink_values, slopes=slopes, window=window)

@@ -39,7 +39,9 @@
 //                           sink (score 0 or learned per head) in the denominator, a block mask or a sliding window
 //   cb_depth_mix            weighted sum over the history of the fp32 stream (+ compute-dtype copy)
 //   cb_poly_norm            a N(z) + b N(z^2) + c N(z^3) + e with N = division by the row's root mean square
-//   cb_head_rmsnorm         RMS norm per head with a weight over the head's channels (query heads | key heads)
+//   cb_head_rmsnorm         RMS norm per head with a weight over the head's channels (query heads | key heads); optionally
+//                           the normed key heads go straight into the paged key cache and the un-normed ones into the
+//                           value cache
 #include "common.cuh"
 
 namespace {
@@ -886,10 +888,18 @@ __global__ void __launch_bounds__(512) poly_norm_kernel(const T* __restrict__ z,
 // the first `heads_a` heads take `wa`, the others `wb` (query heads, then key heads).  One warp per (token, head), fp32;
 // VEC channels per access, the first HEAD_ITEMS vectors of a lane stay in registers between the two passes (1: heads up
 // to 32 x VEC channels, one load per lane and few registers; 8: wide rows such as a query latent).
+// With `k_cache` the key heads do not go to `out`: the normed head is written into the token's row of the paged key cache
+// [blocks, block_size, heads_b, dim] and the head as it came in (before the norm) into the same place of `v_cache` -
+// attention whose values are its un-normed keys gets its query tile and both pages from one pass.
 template <typename T, int VEC, int HEAD_ITEMS>
 __global__ void __launch_bounds__(128) head_rmsnorm_kernel(const T* __restrict__ x, int64_t ldx, T* __restrict__ out,
                                                            int64_t ldo, int64_t tokens, int heads, int heads_a, int dim,
-                                                           const T* __restrict__ wa, const T* __restrict__ wb, float eps) {
+                                                           const T* __restrict__ wa, const T* __restrict__ wb, float eps,
+                                                           T* __restrict__ k_cache, T* __restrict__ v_cache,
+                                                           const int* __restrict__ block_tables,
+                                                           const int* __restrict__ token_seq,
+                                                           const int* __restrict__ token_pos, int block_size,
+                                                           int max_blocks) {
   struct alignas(sizeof(T) * VEC) Pack { T v[VEC]; };
   const int lane = threadIdx.x & 31;
   const int64_t unit = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -916,6 +926,14 @@ __global__ void __launch_bounds__(128) head_rmsnorm_kernel(const T* __restrict__
   }
   const float r = 1.f / sqrtf(warp_sum(ss) / (float)dim + eps);
   T* orow = out + t * ldo + hd * dim;
+  T* vrow = nullptr;
+  if (k_cache != nullptr && hd >= heads_a) {
+    const int seq = token_seq[t], pos = token_pos[t];
+    const int64_t prow = (int64_t)block_tables[(int64_t)seq * max_blocks + pos / block_size] * block_size + pos % block_size;
+    const int64_t at = (prow * (heads - heads_a) + (hd - heads_a)) * dim;
+    orow = k_cache + at;
+    vrow = v_cache + at;
+  }
 #pragma unroll
   for (int it = 0; it < HEAD_ITEMS; ++it) {
     const int i = (lane + 32 * it) * VEC;
@@ -925,6 +943,7 @@ __global__ void __launch_bounds__(128) head_rmsnorm_kernel(const T* __restrict__
 #pragma unroll
       for (int e = 0; e < VEC; ++e) o.v[e] = from_f32<T>(to_f32<T>(keep[it].v[e]) * r * to_f32<T>(ww.v[e]));
       *reinterpret_cast<Pack*>(orow + i) = o;
+      if (vrow != nullptr) *reinterpret_cast<Pack*>(vrow + i) = keep[it];
     }
   }
   for (int i = (lane + 32 * HEAD_ITEMS) * VEC; i < dim; i += 32 * VEC) {
@@ -934,6 +953,7 @@ __global__ void __launch_bounds__(128) head_rmsnorm_kernel(const T* __restrict__
 #pragma unroll
     for (int e = 0; e < VEC; ++e) o.v[e] = from_f32<T>(to_f32<T>(a.v[e]) * r * to_f32<T>(ww.v[e]));
     *reinterpret_cast<Pack*>(orow + i) = o;
+    if (vrow != nullptr) *reinterpret_cast<Pack*>(vrow + i) = a;
   }
 }
 
@@ -2250,24 +2270,27 @@ int cb_poly_norm(const void* z, int64_t ldz, void* out, int64_t tokens, int F, c
 }
 
 int cb_head_rmsnorm(const void* x, int64_t ldx, void* out, int64_t ldo, int64_t tokens, int heads, int heads_a, int dim,
-                    const void* wa, const void* wb, float eps, int dtype, cudaStream_t st) {
+                    const void* wa, const void* wb, float eps, void* k_cache, void* v_cache, const int* block_tables,
+                    const int* token_seq, const int* token_pos, int block_size, int max_blocks, int dtype,
+                    cudaStream_t st) {
   if (tokens == 0 || heads == 0) return 0;
   const int64_t units = tokens * heads;
   CB_DISPATCH_FLOAT(dtype, T, {
     constexpr int V = 8 / sizeof(T);              // 8-byte accesses: a warp covers a head of 128 16-bit channels at once
     const size_t al = V * sizeof(T);
     const bool vec = dim % V == 0 && ldx % V == 0 && ldo % V == 0 && ((uintptr_t)x % al) == 0 && ((uintptr_t)out % al) == 0 &&
-                     ((uintptr_t)wa % al) == 0 && ((uintptr_t)wb % al) == 0;
+                     ((uintptr_t)wa % al) == 0 && ((uintptr_t)wb % al) == 0 && ((uintptr_t)k_cache % al) == 0 &&
+                     ((uintptr_t)v_cache % al) == 0;
+#define CB_HEAD_ARGS (const T*)x, ldx, (T*)out, ldo, tokens, heads, heads_a, dim, (const T*)wa, (const T*)wb, eps,     \
+                     (T*)k_cache, (T*)v_cache, block_tables, token_seq, token_pos, block_size, max_blocks
     const unsigned grid = (unsigned)((units + 3) / 4);
     if (vec && dim <= 32 * V)
-      head_rmsnorm_kernel<T, V, 1><<<grid, 128, 0, st>>>((const T*)x, ldx, (T*)out, ldo, tokens, heads, heads_a, dim,
-                                                         (const T*)wa, (const T*)wb, eps);
+      head_rmsnorm_kernel<T, V, 1><<<grid, 128, 0, st>>>(CB_HEAD_ARGS);
     else if (vec)
-      head_rmsnorm_kernel<T, V, 8><<<grid, 128, 0, st>>>((const T*)x, ldx, (T*)out, ldo, tokens, heads, heads_a, dim,
-                                                         (const T*)wa, (const T*)wb, eps);
+      head_rmsnorm_kernel<T, V, 8><<<grid, 128, 0, st>>>(CB_HEAD_ARGS);
     else
-      head_rmsnorm_kernel<T, 1, 4><<<grid, 128, 0, st>>>((const T*)x, ldx, (T*)out, ldo, tokens, heads, heads_a, dim,
-                                                         (const T*)wa, (const T*)wb, eps);
+      head_rmsnorm_kernel<T, 1, 4><<<grid, 128, 0, st>>>(CB_HEAD_ARGS);
+#undef CB_HEAD_ARGS
   });
   return CB_LAUNCH_CHECK();
 }

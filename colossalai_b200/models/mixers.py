@@ -101,7 +101,13 @@ class BiasSinkAttention(_MixerBase):
             q, k = qk[:, : H * d], qk[:, H * d:]
         if sp.values_from_keys:
             v = k                                          # as they leave the convolution, before the norm
-        if sp.head_norm:
+        if sp.head_norm and sp.values_from_keys:
+            # one pass: normed query heads out, normed key heads into the key pages, un-normed ones into the value pages
+            kc, vc = kv_cache.pages(self.layer_idx)
+            q = mops.head_rms_norm(qk if sp.conv else qkv, H, G, d, self.q_head_norm_weight, self.k_head_norm_weight, eps,
+                                   pages=(kc, vc, kv_cache.block_tables, kv_cache.ragged))
+            k = v = None
+        elif sp.head_norm:
             qk = mops.head_rms_norm(qk if sp.conv else qkv, H, G, d, self.q_head_norm_weight, self.k_head_norm_weight, eps)
             q, k = qk[:, : H * d], qk[:, H * d:]
         if sp.rot_dims or sp.head_unit_norm:

@@ -632,25 +632,45 @@ def poly_norm(z: torch.Tensor, coef: torch.Tensor, eps: float) -> torch.Tensor:
 
 
 def head_rms_norm(x: torch.Tensor, heads_a: int, heads_b: int, dim: int, weight_a: torch.Tensor,
-                  weight_b: Optional[torch.Tensor], eps: float) -> torch.Tensor:
+                  weight_b: Optional[torch.Tensor], eps: float, pages: Optional[tuple] = None) -> torch.Tensor:
     """x [T, >= (heads_a + heads_b) x dim] (unit stride inside a row): every head is divided by its root mean square over
     its `dim` channels and multiplied by a weight [dim] that the heads share - `weight_a` for the first `heads_a` heads
-    (queries), `weight_b` for the next `heads_b` (keys).  Returns a new [T, (heads_a + heads_b) x dim] tensor."""
+    (queries), `weight_b` for the next `heads_b` (keys).  Returns a new [T, (heads_a + heads_b) x dim] tensor.
+
+    `pages` = (k_cache, v_cache [blocks, block_size, heads_b, dim], block_tables, meta): the normed key heads are written
+    into the tokens' rows of `k_cache` and the key heads AS THEY CAME IN into `v_cache` (attention whose values are its keys
+    before their norm); only the query heads [T, heads_a x dim] are returned."""
     T = x.shape[0]
     H = heads_a + heads_b
+    if pages is not None:
+        k_cache, v_cache, block_tables, meta = pages
+        bs = k_cache.shape[1]
+        assert k_cache.shape[2:] == (heads_b, dim) and v_cache.shape == k_cache.shape and k_cache.dtype == x.dtype
     if use_native(x):
         assert x.stride(1) == 1 and weight_a.dtype == x.dtype and (weight_b is None or weight_b.dtype == x.dtype)
-        out = torch.empty(T, H * dim, dtype=x.dtype, device=x.device)
+        out = torch.empty(T, (heads_a if pages is not None else H) * dim, dtype=x.dtype, device=x.device)
+        pargs = (None, None, None, None, None, 0, 0) if pages is None else \
+            (loader.ptr(k_cache), loader.ptr(v_cache), loader.ptr(block_tables), loader.ptr(meta.token_seq),
+             loader.ptr(meta.token_pos), bs, block_tables.shape[1])
+        if pages is not None:
+            assert k_cache.is_contiguous() and v_cache.is_contiguous() and v_cache.dtype == x.dtype
         loader.check(_get_lib().cb_head_rmsnorm(loader.ptr(x), _i64(x.stride(0)), loader.ptr(out), _i64(out.stride(0)),
                                                 _i64(T), H, heads_a, dim, loader.ptr(weight_a), loader.ptr(weight_b), _f(eps),
-                                                code(x.dtype), loader.stream_ptr()), "head_rmsnorm")
+                                                *pargs, code(x.dtype), loader.stream_ptr()), "head_rmsnorm")
         loader.launch_counter.add("head_rmsnorm")
         return out
     y = x[:, : H * dim].float().reshape(T, H, dim)
     y = y / torch.sqrt((y * y).mean(-1, keepdim=True) + eps)
     w = torch.cat([weight_a.float()[None].expand(heads_a, dim)] +
                   ([weight_b.float()[None].expand(heads_b, dim)] if heads_b else []), 0)
-    return (y * w[None]).reshape(T, H * dim).to(x.dtype)
+    y = (y * w[None]).reshape(T, H * dim).to(x.dtype)
+    if pages is None:
+        return y
+    blk = block_tables[meta.token_seq.long(), (meta.token_pos // bs).long()].long()
+    off = (meta.token_pos % bs).long()
+    k_cache.view(k_cache.shape[0], bs, heads_b * dim)[blk, off] = y[:, heads_a * dim:]
+    v_cache.view(v_cache.shape[0], bs, heads_b * dim)[blk, off] = x[:, heads_a * dim: H * dim]
+    return y[:, : heads_a * dim].contiguous()
 
 
 def norm_mean(parts: Sequence[torch.Tensor], weights: Sequence[torch.Tensor], eps: float) -> torch.Tensor:
