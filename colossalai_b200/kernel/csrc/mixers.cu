@@ -2275,14 +2275,14 @@ int cb_head_rmsnorm(const void* x, int64_t ldx, void* out, int64_t ldo, int64_t 
                     cudaStream_t st) {
   if (tokens == 0 || heads == 0) return 0;
   const int64_t units = tokens * heads;
+#define CB_HEAD_ARGS (const T*)x, ldx, (T*)out, ldo, tokens, heads, heads_a, dim, (const T*)wa, (const T*)wb, eps,     \
+                     (T*)k_cache, (T*)v_cache, block_tables, token_seq, token_pos, block_size, max_blocks
   CB_DISPATCH_FLOAT(dtype, T, {
     constexpr int V = 8 / sizeof(T);              // 8-byte accesses: a warp covers a head of 128 16-bit channels at once
     const size_t al = V * sizeof(T);
     const bool vec = dim % V == 0 && ldx % V == 0 && ldo % V == 0 && ((uintptr_t)x % al) == 0 && ((uintptr_t)out % al) == 0 &&
                      ((uintptr_t)wa % al) == 0 && ((uintptr_t)wb % al) == 0 && ((uintptr_t)k_cache % al) == 0 &&
                      ((uintptr_t)v_cache % al) == 0;
-#define CB_HEAD_ARGS (const T*)x, ldx, (T*)out, ldo, tokens, heads, heads_a, dim, (const T*)wa, (const T*)wb, eps,     \
-                     (T*)k_cache, (T*)v_cache, block_tables, token_seq, token_pos, block_size, max_blocks
     const unsigned grid = (unsigned)((units + 3) / 4);
     if (vec && dim <= 32 * V)
       head_rmsnorm_kernel<T, V, 1><<<grid, 128, 0, st>>>(CB_HEAD_ARGS);
@@ -2290,8 +2290,8 @@ int cb_head_rmsnorm(const void* x, int64_t ldx, void* out, int64_t ldo, int64_t 
       head_rmsnorm_kernel<T, V, 8><<<grid, 128, 0, st>>>(CB_HEAD_ARGS);
     else
       head_rmsnorm_kernel<T, 1, 4><<<grid, 128, 0, st>>>(CB_HEAD_ARGS);
-#undef CB_HEAD_ARGS
   });
+#undef CB_HEAD_ARGS
   return CB_LAUNCH_CHECK();
 }
 
