@@ -192,6 +192,15 @@ class ClampedGLU(nn.Module):
         return self.down_proj(ops.clamped_glu(self.gate_up_proj(x), self.limit, self.alpha))
 
 
+def silu_glu(h: torch.Tensor, valid_rows=None) -> torch.Tensor:
+    """silu(gate) * up on packed gate|up rows.  16-bit serving takes the fused kernel (hardware exponential, far inside
+    the rounding of its 16-bit store); 32-bit tensors take IEEE exponentials."""
+    if h.dtype == torch.float32:
+        g, u = h.chunk(2, dim=-1)
+        return F.silu(g) * u
+    return ops.glu(h, "silu", valid_rows=valid_rows if h.is_cuda else None)
+
+
 class SiluGLU(nn.Module):
     """Gated feed-forward without biases: y = W_down (silu(W_gate h) * (W_up h)); gate and up share one GEMM."""
 
@@ -201,7 +210,7 @@ class SiluGLU(nn.Module):
         self.down_proj = nn.Linear(intermediate, cfg.hidden_size, bias=False)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return self.down_proj(ops.glu(self.gate_up_proj(x), "silu"))
+        return self.down_proj(silu_glu(self.gate_up_proj(x)))
 
 
 class ClampedExpertFF(nn.Module):
@@ -229,7 +238,7 @@ class ClampedExpertFF(nn.Module):
 
     def _act(self, h: torch.Tensor, valid_rows) -> torch.Tensor:
         if self.spec.act == "silu":
-            return ops.glu(h, "silu", valid_rows=valid_rows if h.is_cuda else None)
+            return silu_glu(h, valid_rows)
         return ops.clamped_glu(h, self.spec.limit, self.spec.alpha, valid_rows=valid_rows if h.is_cuda else None)
 
     def route(self, x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
