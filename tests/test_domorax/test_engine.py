@@ -38,6 +38,13 @@ MODELS = {
                          O.latent_layer(heads=5, dim=6, rot_dim=10, vdim=6, kv_rank=14, q_rank=30, window=500,
                                         scaling=(8.0, 16, 2.0, 1.0), mlp="dense")],
                  width=30, experts=3, top=3, expert_ff=10, shared_ff=6, ff=21, groups=3, eps=1e-6, residual_mult=0.25),
+    # rows wider than the tensor-core attention kernel takes (a latent row of 272 + 16 columns), heads of its widest row
+    # (256), a delta rule with 256-wide keys, six taps, a window of one position, more experts than a warp has lanes
+    "wide": dict(layers=[O.latent_layer(heads=2, dim=40, rot_dim=16, vdim=24, kv_rank=272, q_rank=24, window=40, mlp="moe"),
+                         O.attention_layer(heads=2, kv_heads=1, dim=256, conv=6, mlp=None),
+                         O.delta_layer(heads=2, kv_heads=1, dim=256, vdim=24, conv=6, mlp="dense"),
+                         O.latent_layer(heads=3, dim=8, rot_dim=8, vdim=8, kv_rank=16, q_rank=8, window=1, mlp="moe")],
+                 width=48, vocab=70, experts=33, top=5, expert_ff=8, shared_ff=8, ff=40, groups=6, eps=1e-5, residual_mult=0.5),
 }
 
 
